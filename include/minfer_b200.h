@@ -1,0 +1,150 @@
+/*
+ * minfer_b200 -- C ABI of the B200 (sm_100a) dynamic sparse prefill attention library.
+ *
+ * Conventions
+ *   - Every pointer named q/k/v/o/plan/..., unless marked "host", is a DEVICE pointer
+ *     owned by the caller.  The library never allocates or frees device memory.
+ *   - `stream` is a cudaStream_t passed as void*; every call only enqueues work on it.
+ *   - Return value: 0 on success, a negative MINF_E_* code when the arguments are
+ *     rejected or a CUDA launch fails (minf_last_error() then holds a message for the
+ *     calling thread).  Problems found on the device (a row block with no usable slash
+ *     offset, an abandoned wait) are reported through the caller's `status` words, which
+ *     the caller zeroes before the first call and may read after synchronising.
+ *   - Tensors are [batch, heads, tokens, head_dim] with head_dim contiguous; the three
+ *     outer strides are given in elements.  head_dim must be 128, dtype bf16.
+ *   - Citations name files of microsoft/MInference v0.1.6.0.
+ */
+#ifndef MINFER_B200_H
+#define MINFER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MINF_OK 0
+#define MINF_E_ARG (-1)      /* invalid argument combination */
+#define MINF_E_CUDA (-2)     /* CUDA runtime / driver error at launch */
+#define MINF_E_UNSUPPORTED (-3)
+
+/* status[] words written by the kernels (caller provides int32_t status[MINF_STATUS_WORDS]) */
+#define MINF_STATUS_WORDS 4
+#define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan */
+#define MINF_ST_NO_SLASH 1   /* number of row blocks whose slash list has no offset < end row */
+#define MINF_ST_AUX0 2
+#define MINF_ST_AUX1 3
+
+/* per-head attention pattern, values of head_mode[] */
+#define MINF_MODE_PLAN 0     /* vertical-slash or block-sparse: tiles and columns come from the plan */
+#define MINF_MODE_ASHAPE 1   /* sink + sliding window, parameters in head_param[] */
+
+const char* minf_version(void);
+const char* minf_last_error(void);
+
+/*
+ * Reference-format index conversion.  Replaces
+ *   minference.cuda.convert_vertical_slash_indexes (csrc/kernels.cpp:7-17,
+ *   csrc/vertical_slash_index.cu:127-167, kernel :27-99).
+ * vertical_indexes [batch, heads, nnz_v] ascending, slash_indexes [batch, heads, nnz_s]
+ * descending, both int32.  Outputs (int32): block_count [batch, heads, rows],
+ * block_offset [batch, heads, rows, nnz_s], column_count [batch, heads, rows],
+ * column_index [batch, heads, rows, nnz_v] with rows = ceil(context_size / 64).  Every
+ * element of the outputs is written (zero tails included), so they need no memset.
+ */
+int minf_convert_vertical_slash_indexes(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    int batch, int heads, int context_size, int nnz_v, int nnz_s,
+    int32_t* block_count, int32_t* block_offset, int32_t* column_count, int32_t* column_index,
+    int32_t* status, void* stream);
+
+/*
+ * Compact plan consumed by minf_sparse_attention_fwd: the same index set as above, kept
+ * as merged [start, end) token ranges plus a bit mask over the head's vertical list
+ * instead of dense per-row-block tables.  `nnz_v_per_head` / `nnz_s_per_head` (int32
+ * [batch*heads], device) give the live length of each head's list inside its
+ * cap_v / cap_s wide row; pass NULL when every head uses the full width.
+ * No counterpart in the reference (it materialises the dense tables per head,
+ * ops/pit_sparse_flash_attention_v2.py:218-224).
+ */
+size_t minf_plan_bytes(int batch, int heads, int context_size, int cap_v, int cap_s);
+int minf_vs_build_plan(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    const int32_t* nnz_v_per_head, const int32_t* nnz_s_per_head,
+    int batch, int heads, int context_size, int cap_v, int cap_s,
+    void* plan, int32_t* status, void* stream);
+
+/*
+ * Block-sparse plan: top-k key blocks per query block from mean-pooled Q and K.  Replaces
+ * _build_block_index (ops/block_sparse_flash_attention.py:151-166) including the padding
+ * rule of its caller (:178).  Only heads whose head_mode entry is MINF_MODE_PLAN and whose
+ * head_select entry is non-zero are written (head_select may be NULL = all heads).
+ * `block_index_out` (optional, int32 [batch, hq, rows_pad, top_k_eff], rows_pad =
+ * (context_size + pad)/64) receives the reference-format sorted block ids.
+ * `scratch` holds minf_block_sparse_scratch_bytes() bytes.
+ */
+size_t minf_block_sparse_scratch_bytes(int batch, int hq, int hkv, int context_size);
+int minf_block_sparse_build_plan(
+    const void* q, const void* k,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim, int top_k,
+    const int32_t* head_select,
+    int cap_v, int cap_s, void* plan, int32_t* block_index_out,
+    void* scratch, int32_t* status, void* stream);
+
+/*
+ * Online vertical/slash index estimation for all heads in one call.  Replaces the torch
+ * ops of vertical_and_slash_kernel (modules/minference_forward.py:599-614) and
+ * sum_all_diagonal_matrix (:110-116): last-64-query x K^T logits, causal mask of the last
+ * block, fp32 softmax, column sums and anti-diagonal sums, +inf forcing of the first 30
+ * columns and the 100 nearest diagonals, per-head top-k.  Outputs are already in the order
+ * the index conversion wants (:218-219 of ops/pit_sparse_flash_attention_v2.py):
+ * v_idx_out [batch, hq, cap_v] ascending, s_idx_out [batch, hq, cap_s] descending offsets.
+ * vertical_size / slash_size: int32 [batch*hq] on the HOST (per-head budgets before
+ * clamping); the clamped live counts are written to nnz_v_out / nnz_s_out (device).
+ * `scratch` holds minf_vs_estimate_scratch_bytes() bytes.
+ */
+size_t minf_vs_estimate_scratch_bytes(int batch, int hq, int context_size);
+int minf_vs_estimate(
+    const void* q, const void* k,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim,
+    const int32_t* vertical_size_host, const int32_t* slash_size_host,
+    int cap_v, int cap_s,
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
+    float* vertical_scores_out, float* slash_scores_out,
+    void* scratch, int32_t* status, void* stream);
+
+/*
+ * Sparse flash-attention forward for all heads in one launch.  Replaces
+ * _triton_mixed_sparse_attention (ops/pit_sparse_flash_attention_v2.py:48-192),
+ * _triton_block_sparse_attention (ops/block_sparse_flash_attention.py:29-148) and the
+ * two-stage streaming kernel (ops/streaming_kernel.py:116-239, 611-646).
+ * K and V may have fewer heads than Q (hq % hkv == 0); query head h reads KV head
+ * h / (hq / hkv).  head_mode [hq] (device, int32, NULL = all MINF_MODE_PLAN) selects the
+ * pattern per head; head_param [hq][2] (device) holds {n_init, n_local} for A-shape heads.
+ * vertical_indexes is the same array given to minf_vs_build_plan (may be NULL when the
+ * plan has no columns).  Output rows >= context_size are never written.
+ */
+int minf_sparse_attention_fwd(
+    const void* q, const void* k, const void* v, void* o,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    const int64_t v_strides[3], const int64_t o_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim, float sm_scale,
+    const int32_t* head_mode, const int32_t* head_param,
+    const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
+    int32_t* status, void* stream);
+
+/*
+ * Number of 64x64 tiles the reference kernels would compute for the index set held in a
+ * plan (block_count + ceil(column_count/64) summed over row blocks and heads) -- the
+ * algorithmic-work figure used for throughput reporting.  tiles_out: uint64 [1], device.
+ */
+int minf_plan_count_tiles(const void* plan, int batch, int heads, int context_size,
+                          int cap_v, int cap_s, unsigned long long* tiles_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINFER_B200_H */

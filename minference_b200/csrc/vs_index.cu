@@ -1,0 +1,278 @@
+// Vertical/slash index conversion, one warp per 64-row query block.
+//
+// Replaces convert_vertical_slash_indexes_kernel (csrc/vertical_slash_index.cu:27-99 of the
+// reference), which walks the two sorted lists with one thread per row block.  The
+// sequential merge there has a closed form that a warp can evaluate 32 entries at a time:
+//
+//   * Slash offset o maps to the end token e = max(end_m - o, 64) of a 64-wide tile; with
+//     offsets sorted descending, e is non-decreasing.
+//   * While a range that started at e0 keeps growing, its end after seeing e is
+//     e0 + 64*ceil((e - e0)/64) (the reference grows it by exactly 64 whenever e passes the
+//     current end).  A new range starts at entry j iff e_j > end(e_{j-1}) + 64.
+//   * Hence only entries with e_j - e_{j-1} > 64 can start a range; a ballot finds them and
+//     the warp resolves them in order, everything else needs no work.
+//   * A vertical column is gathered iff it lies below the start of the last range and in
+//     none of the ranges; since both lists are sorted this is a forward scan, done 32
+//     columns per step with ballots.
+//
+// Two output formats from the same walk:
+//   REF  -- the reference's dense tables (block_count/block_offset/column_count/column_index),
+//           bit-exact including zero tails;
+//   PLAN -- merged [start,end) ranges + a bit mask over the vertical list (plan_layout.h).
+#include <climits>
+
+#include "common.h"
+#include "plan_layout.h"
+
+namespace minf {
+
+constexpr int kConvertWarps = 8;
+constexpr int kMaxBitWordsPerLane = 8;  // vertical lists up to 8192 entries in PLAN mode
+
+struct ConvertArgs {
+    const int32_t* seqlens;
+    const int32_t* v_idx;
+    const int32_t* s_idx;
+    const int32_t* nnz_v_per_head;
+    const int32_t* nnz_s_per_head;
+    int heads, rows, cap_v, cap_s;
+    // REF outputs
+    int32_t* block_count;
+    int32_t* block_offset;
+    int32_t* column_count;
+    int32_t* column_index;
+    // PLAN output
+    unsigned char* plan;
+    PlanLayout layout;
+    int32_t* status;
+};
+
+template <bool REF>
+__global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const ConvertArgs a) {
+    extern __shared__ int32_t lists[];
+    int32_t* s_list = lists;
+    int32_t* v_list = lists + a.cap_s;
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int bh = b * a.heads + h;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nnz_s = a.nnz_s_per_head ? min(a.nnz_s_per_head[bh], a.cap_s) : a.cap_s;
+    const int nnz_v = a.nnz_v_per_head ? min(a.nnz_v_per_head[bh], a.cap_v) : a.cap_v;
+
+    for (int i = threadIdx.x; i < nnz_s; i += blockDim.x) s_list[i] = a.s_idx[(size_t)bh * a.cap_s + i];
+    for (int i = threadIdx.x; i < nnz_v; i += blockDim.x) v_list[i] = a.v_idx[(size_t)bh * a.cap_v + i];
+    __syncthreads();
+
+    const int m = blockIdx.x * kConvertWarps + warp;
+    if (m >= a.rows) return;
+    const int seqlen = a.seqlens[b];
+    const int start_m = m * 64, end_m = start_m + 64;
+    const size_t row = (size_t)bh * a.rows + m;
+
+    int32_t* bo = nullptr;
+    int32_t* ci = nullptr;
+    int2* rng = nullptr;
+    if (REF) {
+        bo = a.block_offset + row * a.cap_s;
+        ci = a.column_index + row * a.cap_v;
+    } else {
+        rng = reinterpret_cast<int2*>(a.plan + (size_t)bh * a.layout.head_bytes + a.layout.rng_off) +
+              plan_rng_index(m, a.layout.cap_s);
+    }
+
+    int nblk = 0, ncol = 0, nrng = 0, vp = 0;
+    uint32_t bits[kMaxBitWordsPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxBitWordsPerLane; ++i) bits[i] = 0u;
+
+    // first slash entry below end_m (list is descending): lower bound, uniform across lanes
+    int i0 = nnz_s;
+    if (start_m < seqlen) {
+        int lo = 0, hi = nnz_s;
+        while (lo < hi) {
+            int mid = (lo + hi) >> 1;
+            if (s_list[mid] >= end_m) lo = mid + 1; else hi = mid;
+        }
+        i0 = lo;
+        if (i0 == nnz_s && lane == 0) atomicAdd(a.status + MINF_ST_NO_SLASH, 1);
+    }
+
+    if (i0 < nnz_s) {
+        // close range [rs, re): emit its tiles / record it, then advance through the verticals
+        auto close_range = [&](int rs, int re) {
+            if (REF) {
+                for (int t = rs + 64 * lane; t < re; t += 64 * 32) bo[nblk + ((t - rs) >> 6)] = t;
+                nblk += (re - rs) >> 6;
+            } else {
+                if (lane == 0) rng[nrng] = make_int2(rs, re);
+                ++nrng;
+            }
+            for (;;) {
+                const int i = vp + lane;
+                const int val = i < nnz_v ? v_list[i] : INT_MAX;
+                const int n_below = __popc(__ballot_sync(0xffffffffu, val < rs));
+                if (REF) {
+                    if (lane < n_below) ci[ncol + lane] = val;
+                    ncol += n_below;
+                } else if (n_below) {
+                    const int lo_bit = vp, hi_bit = vp + n_below;
+#pragma unroll
+                    for (int w = 0; w < kMaxBitWordsPerLane; ++w) {
+                        const int base = 32 * (lane + 32 * w);
+                        const int lo = max(lo_bit, base), hi = min(hi_bit, base + 32);
+                        if (lo < hi) {
+                            const int n = hi - lo;
+                            bits[w] |= (n == 32 ? 0xffffffffu : ((1u << n) - 1u)) << (lo - base);
+                        }
+                    }
+                }
+                const int n_inside = __popc(__ballot_sync(0xffffffffu, val < re));
+                vp += n_inside;
+                if (n_inside < 32) break;
+            }
+        };
+
+        int e_first = max(end_m - s_list[i0], 64);
+        int carry = e_first;
+        for (int base = i0; base < nnz_s; base += 32) {
+            const int i = base + lane;
+            const bool valid = i < nnz_s;
+            const int e = valid ? max(end_m - s_list[i], 64) : INT_MAX;
+            int prev = __shfl_up_sync(0xffffffffu, e, 1);
+            if (lane == 0) prev = carry;
+            unsigned cand = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
+            while (cand) {
+                const int j = __ffs(cand) - 1;
+                cand &= cand - 1;
+                const int ej = __shfl_sync(0xffffffffu, e, j);
+                const int pj = __shfl_sync(0xffffffffu, prev, j);
+                const int re = e_first + ((pj - e_first + 63) & ~63);
+                if (ej > re + 64) {
+                    close_range(e_first - 64, re);
+                    e_first = ej;
+                }
+            }
+            const int last = min(31, nnz_s - 1 - base);
+            carry = __shfl_sync(0xffffffffu, e, last);
+        }
+        close_range(e_first - 64, e_first + ((carry - e_first + 63) & ~63));
+    }
+
+    if (REF) {
+        if (lane == 0) {
+            a.block_count[row] = nblk;
+            a.column_count[row] = ncol;
+        }
+        for (int j = nblk + lane; j < a.cap_s; j += 32) bo[j] = 0;
+        for (int j = ncol + lane; j < a.cap_v; j += 32) ci[j] = 0;
+    } else {
+        unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
+        if (lane == 0) reinterpret_cast<int32_t*>(slot)[m] = nrng;
+        uint32_t* wb = reinterpret_cast<uint32_t*>(slot + a.layout.bits_off) + (size_t)m * a.layout.words_v;
+#pragma unroll
+        for (int w = 0; w < kMaxBitWordsPerLane; ++w) {
+            const int idx = lane + 32 * w;
+            if (idx < a.layout.words_v) wb[idx] = bits[w];
+        }
+    }
+}
+
+__global__ void plan_count_tiles_kernel(const unsigned char* plan, PlanLayout L, int total_rows,
+                                        unsigned long long* out) {
+    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long tiles = 0;
+    if (gid < total_rows) {
+        const int bh = (int)(gid / L.rows), m = (int)(gid % L.rows);
+        const unsigned char* slot = plan + (size_t)bh * L.head_bytes;
+        const int n = reinterpret_cast<const int32_t*>(slot)[m];
+        const int2* rng = reinterpret_cast<const int2*>(slot + L.rng_off) + plan_rng_index(m, L.cap_s);
+        for (int i = 0; i < n; ++i) tiles += (rng[i].y - rng[i].x) >> 6;
+        const uint32_t* wb = reinterpret_cast<const uint32_t*>(slot + L.bits_off) + (size_t)m * L.words_v;
+        int cols = 0;
+        for (int w = 0; w < L.words_v; ++w) cols += __popc(wb[w]);
+        tiles += (cols + 63) >> 6;
+    }
+    // warp reduce then one atomic per warp
+    for (int o = 16; o; o >>= 1) tiles += __shfl_down_sync(0xffffffffu, tiles, o);
+    if ((threadIdx.x & 31) == 0 && tiles) atomicAdd(out, tiles);
+}
+
+static int launch_convert(bool ref, const ConvertArgs& a, int batch, cudaStream_t st) {
+    const size_t smem = (size_t)(a.cap_s + a.cap_v) * sizeof(int32_t);
+    if (smem > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "index lists too long for shared memory (%zu bytes)", smem);
+    dim3 grid((a.rows + kConvertWarps - 1) / kConvertWarps, a.heads, batch);
+    if (ref) {
+        MINF_CUDA_OK(cudaFuncSetAttribute(vs_convert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        vs_convert_kernel<true><<<grid, kConvertWarps * 32, smem, st>>>(a);
+    } else {
+        MINF_CUDA_OK(cudaFuncSetAttribute(vs_convert_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        vs_convert_kernel<false><<<grid, kConvertWarps * 32, smem, st>>>(a);
+    }
+    MINF_LAUNCH_OK("vs_convert_kernel");
+    return MINF_OK;
+}
+
+}  // namespace minf
+
+using namespace minf;
+
+extern "C" int minf_convert_vertical_slash_indexes(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    int batch, int heads, int context_size, int nnz_v, int nnz_s,
+    int32_t* block_count, int32_t* block_offset, int32_t* column_count, int32_t* column_index,
+    int32_t* status, void* stream) {
+    if (!seqlens || !vertical_indexes || !slash_indexes || !block_count || !block_offset || !column_count ||
+        !column_index || !status)
+        return fail(MINF_E_ARG, "null pointer argument");
+    if (batch < 1 || heads < 1 || context_size < 1 || nnz_v < 1 || nnz_s < 1 || heads > 65535 || batch > 65535)
+        return fail(MINF_E_ARG, "bad sizes: batch=%d heads=%d context=%d nnz_v=%d nnz_s=%d", batch, heads,
+                    context_size, nnz_v, nnz_s);
+    ConvertArgs a{};
+    a.seqlens = seqlens; a.v_idx = vertical_indexes; a.s_idx = slash_indexes;
+    a.heads = heads; a.rows = (context_size + 63) / 64; a.cap_v = nnz_v; a.cap_s = nnz_s;
+    a.block_count = block_count; a.block_offset = block_offset;
+    a.column_count = column_count; a.column_index = column_index;
+    a.status = status;
+    return launch_convert(true, a, batch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t minf_plan_bytes(int batch, int heads, int context_size, int cap_v, int cap_s) {
+    if (batch < 1 || heads < 1 || context_size < 1 || cap_v < 0 || cap_s < 1) return 0;
+    return (size_t)make_plan_layout(context_size, cap_v, cap_s).head_bytes * batch * heads;
+}
+
+extern "C" int minf_vs_build_plan(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    const int32_t* nnz_v_per_head, const int32_t* nnz_s_per_head,
+    int batch, int heads, int context_size, int cap_v, int cap_s,
+    void* plan, int32_t* status, void* stream) {
+    if (!seqlens || !vertical_indexes || !slash_indexes || !plan || !status)
+        return fail(MINF_E_ARG, "null pointer argument");
+    if (batch < 1 || heads < 1 || context_size < 1 || cap_v < 1 || cap_s < 1 || heads > 65535 || batch > 65535)
+        return fail(MINF_E_ARG, "bad sizes: batch=%d heads=%d context=%d cap_v=%d cap_s=%d", batch, heads,
+                    context_size, cap_v, cap_s);
+    if (cap_v > 32 * 32 * kMaxBitWordsPerLane)
+        return fail(MINF_E_UNSUPPORTED, "cap_v=%d exceeds %d", cap_v, 32 * 32 * kMaxBitWordsPerLane);
+    ConvertArgs a{};
+    a.seqlens = seqlens; a.v_idx = vertical_indexes; a.s_idx = slash_indexes;
+    a.nnz_v_per_head = nnz_v_per_head; a.nnz_s_per_head = nnz_s_per_head;
+    a.heads = heads; a.rows = (context_size + 63) / 64; a.cap_v = cap_v; a.cap_s = cap_s;
+    a.plan = static_cast<unsigned char*>(plan);
+    a.layout = make_plan_layout(context_size, cap_v, cap_s);
+    a.status = status;
+    return launch_convert(false, a, batch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int minf_plan_count_tiles(const void* plan, int batch, int heads, int context_size,
+                                     int cap_v, int cap_s, unsigned long long* tiles_out, void* stream) {
+    if (!plan || !tiles_out) return fail(MINF_E_ARG, "null pointer argument");
+    PlanLayout L = make_plan_layout(context_size, cap_v, cap_s);
+    const long long total = (long long)L.rows * batch * heads;
+    if (total > INT_MAX) return fail(MINF_E_UNSUPPORTED, "too many row blocks");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    MINF_CUDA_OK(cudaMemsetAsync(tiles_out, 0, sizeof(unsigned long long), st));
+    plan_count_tiles_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        static_cast<const unsigned char*>(plan), L, (int)total, tiles_out);
+    MINF_LAUNCH_OK("plan_count_tiles_kernel");
+    return MINF_OK;
+}
