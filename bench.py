@@ -1,0 +1,307 @@
+"""Benchmark of the dynamic sparse prefill attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One *step* is one pass of the hot path over one layer of synthetic input: online
+vertical/slash index estimation -> index plan -> sparse flash-attention forward, for all
+heads.  Default workload: Llama-3-8B layer shape at 131072 tokens (32 query / 8 KV heads,
+head_dim 128, bf16, vertical 1000 / slash 6096 / last_q 64 on every head), seeded N(0,1)
+Q/K/V with rotary embedding and planted sink columns standing in for real prompts.
+
+Printed JSON (one line, rank 0):
+  value        algorithmic TFLOP/s with inputs resident in HBM: 64x64 tiles of the reference
+               index set x 4*64*64*128 flop / step time
+  e2e          the same through the public operator (minference_prefill_forward) with HOST
+               buffers: pinned Q/K/V copied in and the output copied out inside the timed region
+  roofline     the attention kernel alone (CUDA events around its launch, same stream)
+  cpu_baseline the CPU oracle (port of the reference's torch path) on a bounded sample
+
+With N > 1 ranks every rank runs the same workload on its own seeded data (replicas: the
+single-GPU path has no exchange step); the value is the sum of the work over the slowest rank's time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FLOP_PER_TILE = 4 * 64 * 64 * 128
+
+WORKLOADS = {
+    # name: (tokens, query heads, kv heads, vertical, slash)
+    "llama3_8b_128k_vs": (131072, 32, 8, 1000, 6096),
+    "llama3_8b_32k_vs": (32768, 32, 8, 1000, 6096),
+    "llama3_8b_8k_vs": (8192, 32, 8, 1000, 6096),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"burst": p["bf16_tflops"], "sustained": p["bf16_tflops_sustained"], "hbm": p["hbm_gbs"], "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+
+def cpu_sample(n, hq, hkv, vsize, ssize, seed, budget_s=12.0, max_blocks=24):
+    """Time the CPU oracle on a bounded sample of the workload: one head's estimator over the
+    full context, its index conversion, and masked-dense attention for a spread of 64-row
+    blocks (evaluated until `budget_s` seconds are used).  Returns (TFLOP/s, description)."""
+    import numpy as np
+    from minference_b200.synthetic import make_qkv
+    from oracle import reference_math as R
+
+    q, k, v = make_qkv(n, 1, 1, seed=seed, dtype=torch.float32)
+    t0 = time.perf_counter()
+    v_idx, s_idx = R.vertical_slash_estimate(q, k, vsize, ssize)
+    vs, ss = R.presort_indices(v_idx, s_idx, 1, 1)
+    bc, bo, cc, ci = R.convert_vertical_slash_indexes(np.full((1,), n, np.int32), vs.numpy(), ss.numpy(), n)
+    t_index = time.perf_counter() - t0
+    rows = (n + 63) // 64
+    order = [rows - 1 - (i * 7919) % rows for i in range(rows)]      # spread over the context, last block first
+    tiles = 0
+    done = 0
+    t1 = time.perf_counter()
+    for m in order[:max_blocks]:
+        r0, r1 = m * 64, min(m * 64 + 64, n)
+        mask = R.vs_mask_for_rows(bc[0, 0], bo[0, 0], cc[0, 0], ci[0, 0], n, [m])[: r1 - r0, :r1]
+        R.masked_attention_rows(q[0, 0, r0:r1], k[0, 0, :r1], v[0, 0, :r1], mask, r0)
+        tiles += int(bc[0, 0, m]) + (int(cc[0, 0, m]) + 63) // 64
+        done += 1
+        if time.perf_counter() - t1 > budget_s:
+            break
+    t_attn = time.perf_counter() - t1
+    # the index work of one head is amortised over all of its row blocks
+    t_total = t_attn + t_index * done / rows
+    desc = (f"1 of {hq} heads, {done} of {rows} row blocks (64 query rows each, spread over the context) of masked-dense "
+            f"fp32 attention + that share of the head's estimator and index conversion; {t_attn + t_index:.1f} s of CPU work")
+    return tiles * FLOP_PER_TILE / t_total / 1e12, desc
+
+
+def run_reference_arm(args, wl):
+    n, hq, hkv, vsize, ssize = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    vals = []
+    desc = ""
+    t_begin = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        per_step_budget = max(2.0, min(12.0, 150.0 / (args.warmup + args.steps)))
+        tf, desc = cpu_sample(n, hq, hkv, vsize, ssize, seed=i, budget_s=per_step_budget)
+        if i >= args.warmup:
+            vals.append(tf)
+    value = sum(vals) / len(vals)
+    cores = torch.get_num_threads()
+    out = {
+        "impl": "reference", "metric": "sparse_prefill_attn_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * (time.perf_counter() - t_begin) / (args.warmup + args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, "tokens": n, "q_heads": hq, "kv_heads": hkv, "vertical": vsize, "slash": ssize},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out))
+
+
+# ------------------------------------------------------------------------------ GPU arm
+
+def run_gpu_arm(args, wl):
+    import torch.distributed as dist
+
+    from minference_b200 import _cabi
+    from minference_b200.cuda import set_status_checks
+    from minference_b200.modules.minference_forward import minference_prefill_forward, vertical_slash_estimate
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import make_qkv
+
+    n, hq, hkv, vsize, ssize = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _cabi.lib()     # fail loudly right here when the CUDA library is missing
+    set_status_checks(False)    # status words are read once after the timed region instead
+
+    q, k, v = make_qkv(n, hq, hkv, seed=rank, dtype=torch.bfloat16, device=dev)
+    cfg = {"attn_forward_config": {"best_pattern": [{str(h): ["vertical_and_slash", vsize, ssize, 1.0] for h in range(hq)}]},
+           "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    attn_events, est_events, plan_events = [], [], []
+    tiles_box = {}
+
+    def step_resident(record: bool):
+        e0, e1, e2, e3 = ev(), ev(), ev(), ev()
+        e0.record()
+        v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, vsize, ssize)
+        e1.record()
+        plan = build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)
+        e2.record()
+        out = sparse_attention_forward(q, k, v, plan)
+        e3.record()
+        if record:
+            est_events.append((e0, e1)); plan_events.append((e1, e2)); attn_events.append((e2, e3))
+        tiles_box["plan"] = plan
+        return out
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_resident(False)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    t0, t1 = ev(), ev()
+    t0.record()
+    for _ in range(args.steps):
+        step_resident(True)
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = t0.elapsed_time(t1)
+    plan = tiles_box["plan"]
+    status = plan.status.tolist()
+    if status[0] != 0 or status[1] != 0:
+        raise SystemExit(f"device status {status}: the kernels reported an error")
+    tiles = plan.count_tiles()
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
+    est_ms = sum(a.elapsed_time(b) for a, b in est_events) / len(est_events)
+    plan_ms = sum(a.elapsed_time(b) for a, b in plan_events) / len(plan_events)
+
+    # ---- end to end through the public operator with host buffers
+    hq_, hk_, hv_ = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq_).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def step_e2e():
+        dq.copy_(hq_, non_blocking=True); dk.copy_(hk_, non_blocking=True); dv.copy_(hv_, non_blocking=True)
+        out = minference_prefill_forward(dq, dk, dv, cfg)
+        ho.copy_(out, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    step_e2e()
+    barrier()
+    s0, s1 = ev(), ev()
+    s0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    s1.record()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1) / e2e_steps
+    parity_probe = float((ho[0, 0, -1].float() - step_resident(False)[0, 0, -1].float().cpu()).abs().max())
+
+    times = torch.tensor([total_ms, e2e_ms, attn_ms], dtype=torch.float64, device=dev)
+    tile_sum = torch.tensor([float(tiles)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tile_sum, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, attn_ms_max = times.tolist()
+    all_tiles = tile_sum.item()
+    ms_per_step = total_ms / args.steps
+    value = all_tiles * FLOP_PER_TILE / (ms_per_step * 1e-3) / 1e12
+    e2e_value = all_tiles * FLOP_PER_TILE / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = tiles * FLOP_PER_TILE / (attn_ms * 1e-3) / 1e12
+        cpu_tf, cpu_desc = cpu_sample(n, hq, hkv, vsize, ssize, seed=0, budget_s=12.0)
+        rows = (n + 63) // 64
+        out = {
+            "metric": "sparse_prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl, "tokens": n, "q_heads": hq, "kv_heads": hkv, "head_dim": 128, "vertical": vsize,
+                       "slash": ssize, "last_q": 64, "l2": "inputs_exceed_l2", "replicas": world,
+                       "tiles_per_layer": tiles, "fraction_of_causal_tiles": tiles / (hq * rows * (rows + 1) / 2),
+                       "dense_equivalent_tflops": 4.0 * (n * n / 2) * 128 * hq * world / (ms_per_step * 1e-3) / 1e12,
+                       "ms_estimator": est_ms, "ms_plan": plan_ms, "ms_attention": attn_ms},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (q, k, v)),
+                    "d2h_bytes_per_step": q.numel() * q.element_size(), "max_abs_vs_resident_last_row": parity_probe},
+            "gpu_launches": 5 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "sparse_attn_fwd_kernel", "achieved": achieved,
+                         "peak": peaks["sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["sustained"],
+                         "peak_kind": f"bf16 dense sustained, of {peaks['source']}", "frac_of_burst": achieved / peaks["burst"],
+                         "traffic": None},
+            "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": cpu_desc},
+            "clocks": clocks,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_128k_vs", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args, args.workload)
+    else:
+        run_gpu_arm(args, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -101,8 +101,12 @@ int minf_block_sparse_build_plan(
  * columns and the 100 nearest diagonals, per-head top-k.  Outputs are already in the order
  * the index conversion wants (:218-219 of ops/pit_sparse_flash_attention_v2.py):
  * v_idx_out [batch, hq, cap_v] ascending, s_idx_out [batch, hq, cap_s] descending offsets.
- * vertical_size / slash_size: int32 [batch*hq] on the HOST (per-head budgets before
- * clamping); the clamped live counts are written to nnz_v_out / nnz_s_out (device).
+ * vertical_size / slash_size: int32 [batch*hq] on the device, per-head budgets before the
+ * reference's clamping (:600); a negative budget skips the head (nnz = -1 is written, and
+ * minf_vs_build_plan leaves heads with a negative slash count untouched).  The clamped
+ * live counts are written to nnz_v_out / nnz_s_out.  vertical_scores_out /
+ * slash_scores_out (optional, fp32 [batch, hq, context_size]; slash indexed by diagonal
+ * offset) receive the raw scores.
  * `scratch` holds minf_vs_estimate_scratch_bytes() bytes.
  */
 size_t minf_vs_estimate_scratch_bytes(int batch, int hq, int context_size);
@@ -110,7 +114,7 @@ int minf_vs_estimate(
     const void* q, const void* k,
     const int64_t q_strides[3], const int64_t k_strides[3],
     int batch, int hq, int hkv, int context_size, int head_dim,
-    const int32_t* vertical_size_host, const int32_t* slash_size_host,
+    const int32_t* vertical_size, const int32_t* slash_size,
     int cap_v, int cap_s,
     int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
     float* vertical_scores_out, float* slash_scores_out,

@@ -1,0 +1,250 @@
+// Block-sparse index estimation: top-k key blocks per 64-row query block from mean-pooled
+// Q and K.  Replaces _build_block_index (ops/block_sparse_flash_attention.py:151-166 of the
+// reference: reshape+mean, a [rows, rows] einsum, block-causal mask, torch.topk, sort) and the
+// padding rule of its caller (:178: the sequence is padded by 64 - (N & 63) rows, a whole
+// extra block of zeros when N is a multiple of 64).
+//
+//   pool kernel    one warp per (tensor, batch, head, block): fp32 mean of up to 64 rows,
+//                  rounded to bf16 like the reference's bf16 mean.  HBM-bound: reads Q and K once.
+//   select kernel  one CTA per (batch, head, query block m): scores of key blocks 0..m (fp32
+//                  dot of the pooled bf16 vectors, rounded to bf16 like the reference's bf16
+//                  einsum) in shared memory, radix select of the k-th largest, ordered
+//                  compaction.  Equal scores at the threshold: lowest block index first
+//                  (torch.topk leaves this unspecified).  Writes the reference-format sorted
+//                  block ids and/or the merged token ranges of the attention plan.
+#include <cuda_bf16.h>
+
+#include "common.h"
+#include "plan_layout.h"
+
+namespace minf {
+
+struct PoolArgs {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k;
+    long long q_sb, q_sh, q_sn, k_sb, k_sh, k_sn;
+    int batch, hq, hkv, n_ctx, rows_pad;
+    __nv_bfloat16* qpool;   // [batch, hq, rows_pad, 128]
+    __nv_bfloat16* kpool;   // [batch, hkv, rows_pad, 128]
+};
+
+__global__ void __launch_bounds__(256) bs_pool_kernel(const PoolArgs a) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const long long nq = (long long)a.batch * a.hq * a.rows_pad;
+    const long long nk = (long long)a.batch * a.hkv * a.rows_pad;
+    if (warp >= nq + nk) return;
+    const bool is_k = warp >= nq;
+    const long long id = is_k ? warp - nq : warp;
+    const int heads = is_k ? a.hkv : a.hq;
+    const int m = (int)(id % a.rows_pad);
+    const int h = (int)((id / a.rows_pad) % heads);
+    const int b = (int)(id / ((long long)a.rows_pad * heads));
+    const __nv_bfloat16* src = is_k ? a.k + b * a.k_sb + h * a.k_sh : a.q + b * a.q_sb + h * a.q_sh;
+    const long long sn = is_k ? a.k_sn : a.q_sn;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int r_hi = min(64 * m + 64, a.n_ctx);
+    for (int r = 64 * m; r < r_hi; ++r) {     // padded rows are zeros: they only count in the divisor
+        const uint2 raw = *reinterpret_cast<const uint2*>(src + r * sn + 4 * lane);
+        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        acc[0] += __bfloat162float(p0.x); acc[1] += __bfloat162float(p0.y);
+        acc[2] += __bfloat162float(p1.x); acc[3] += __bfloat162float(p1.y);
+    }
+    __nv_bfloat16* dst = (is_k ? a.kpool : a.qpool) + id * 128 + 4 * lane;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = __float2bfloat16_rn(acc[i] * (1.f / 64.f));
+}
+
+struct BsSelectArgs {
+    const __nv_bfloat16* qpool;
+    const __nv_bfloat16* kpool;
+    int batch, hq, hkv, n_ctx, rows, rows_pad, top_k;   // top_k already clamped to rows_pad
+    const int32_t* head_select;
+    int32_t* block_index;    // optional [batch, hq, rows_pad, top_k]
+    unsigned char* plan;     // optional
+    PlanLayout layout;
+};
+
+// order-preserving map of a float to uint32
+__device__ __forceinline__ uint32_t float_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
+    extern __shared__ uint32_t keys[];        // rows_pad score keys
+    __shared__ float qv[128];
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t sh_prefix, sh_remaining;
+    __shared__ int warp_cnt[8];
+    __shared__ int sh_base, sh_ties;
+    __shared__ unsigned char take_flag[256];
+
+    const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    if (a.head_select && a.head_select[h] == 0) return;
+    const int hk = h / (a.hq / a.hkv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t bh = (size_t)b * a.hq + h;
+    const int n_blocks = m + 1;               // causal key blocks 0..m
+    const int k = min(a.top_k, n_blocks);     // blocks the attention kernel consumes (:81)
+
+    if (threadIdx.x < 128) qv[threadIdx.x] = __bfloat162float(a.qpool[(bh * a.rows_pad + m) * 128 + threadIdx.x]);
+    __syncthreads();
+    const __nv_bfloat16* kp = a.kpool + ((size_t)b * a.hkv + hk) * a.rows_pad * 128;
+    for (int n = warp; n < n_blocks; n += 8) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(kp + (size_t)n * 128 + 4 * lane);
+        const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        float s = qv[4 * lane] * __bfloat162float(p0.x) + qv[4 * lane + 1] * __bfloat162float(p0.y) +
+                  qv[4 * lane + 2] * __bfloat162float(p1.x) + qv[4 * lane + 3] * __bfloat162float(p1.y);
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) keys[n] = float_key(__bfloat162float(__float2bfloat16_rn(s)));
+    }
+    __syncthreads();
+
+    uint32_t thr = 0;
+    int ties_needed = 0;
+    if (k < n_blocks) {
+        uint32_t prefix = 0, prefix_mask = 0, remaining = k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            hist[threadIdx.x] = 0;
+            __syncthreads();
+            for (int n = threadIdx.x; n < n_blocks; n += blockDim.x)
+                if ((keys[n] & prefix_mask) == prefix) atomicAdd(&hist[(keys[n] >> shift) & 255u], 1u);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                uint32_t rem = remaining;
+                int d = 255;
+                for (; d > 0; --d) {
+                    if (hist[d] >= rem) break;
+                    rem -= hist[d];
+                }
+                sh_prefix = prefix | ((uint32_t)d << shift);
+                sh_remaining = rem;
+            }
+            __syncthreads();
+            prefix = sh_prefix;
+            remaining = sh_remaining;
+            prefix_mask |= 255u << shift;
+            __syncthreads();
+        }
+        thr = prefix;
+        ties_needed = (int)remaining;
+    }
+
+    // ordered compaction of the selected block ids (ascending), 256 candidates per round
+    int32_t* bi = a.block_index ? a.block_index + (bh * a.rows_pad + m) * a.top_k : nullptr;
+    int2* rng = nullptr;
+    if (a.plan && m < a.rows)
+        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_index(m, a.layout.cap_s);
+    if (threadIdx.x == 0) { sh_base = 0; sh_ties = 0; }
+    __syncthreads();
+    int nrng = 0;          // maintained by thread 0 only
+    int cur_lo = -1, cur_hi = -1;
+    for (int start = 0; start < n_blocks; start += 256) {
+        const int n = start + threadIdx.x;
+        const bool in = n < n_blocks;
+        const bool tie = in && k < n_blocks && keys[n] == thr;
+        const unsigned tb = __ballot_sync(0xffffffffu, tie);
+        if (lane == 0) warp_cnt[warp] = __popc(tb);
+        __syncthreads();
+        int tie_rank = sh_ties + __popc(tb & ((1u << lane) - 1u));
+        int round_ties = 0;
+        for (int w = 0; w < 8; ++w) { if (w < warp) tie_rank += warp_cnt[w]; round_ties += warp_cnt[w]; }
+        __syncthreads();
+        const bool take = in && (k >= n_blocks || keys[n] > thr || (tie && tie_rank < ties_needed));
+        const unsigned kb = __ballot_sync(0xffffffffu, take);
+        if (lane == 0) warp_cnt[warp] = __popc(kb);
+        __syncthreads();
+        int dst = sh_base + __popc(kb & ((1u << lane) - 1u));
+        int round_take = 0;
+        for (int w = 0; w < 8; ++w) { if (w < warp) dst += warp_cnt[w]; round_take += warp_cnt[w]; }
+        if (take && bi) bi[dst] = n;
+        take_flag[threadIdx.x] = take ? 1 : 0;   // staged so thread 0 can merge adjacent blocks into ranges
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            sh_base += round_take;
+            sh_ties += round_ties;
+            if (rng) {
+                const int hi = min(start + 256, n_blocks);
+                for (int n2 = start; n2 < hi; ++n2) {
+                    if (!take_flag[n2 - start]) continue;
+                    if (n2 * 64 == cur_hi) cur_hi += 64;
+                    else {
+                        if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
+                        cur_lo = n2 * 64; cur_hi = cur_lo + 64;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && rng) {
+        if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
+        reinterpret_cast<int32_t*>(a.plan + bh * a.layout.head_bytes)[m] = nrng;
+    }
+    if (a.plan && m < a.rows) {
+        uint32_t* wb = reinterpret_cast<uint32_t*>(a.plan + bh * a.layout.head_bytes + a.layout.bits_off) + (size_t)m * a.layout.words_v;
+        for (int w = threadIdx.x; w < a.layout.words_v; w += blockDim.x) wb[w] = 0u;
+    }
+    // tail of the reference-format row: the reference holds arbitrary masked block ids there
+    // (ties among -inf scores); the first causally masked ids in ascending order are used here
+    if (bi) {
+        for (int j = k + threadIdx.x; j < a.top_k; j += blockDim.x) bi[j] = min(n_blocks + (j - k), a.rows_pad - 1);
+    }
+}
+
+}  // namespace minf
+
+using namespace minf;
+
+static int bs_rows_pad(int n) { return (n + (64 - (n & 63))) / 64; }
+
+extern "C" size_t minf_block_sparse_scratch_bytes(int batch, int hq, int hkv, int context_size) {
+    if (batch < 1 || hq < 1 || hkv < 1 || context_size < 1) return 0;
+    return (size_t)batch * (hq + hkv) * bs_rows_pad(context_size) * 128 * sizeof(__nv_bfloat16) + 256;
+}
+
+extern "C" int minf_block_sparse_build_plan(
+    const void* q, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim, int top_k,
+    const int32_t* head_select, int cap_v, int cap_s, void* plan, int32_t* block_index_out,
+    void* scratch, int32_t* status, void* stream) {
+    (void)status;
+    if (!q || !k || !scratch || (!plan && !block_index_out)) return fail(MINF_E_ARG, "null pointer argument");
+    if (head_dim != 128) return fail(MINF_E_UNSUPPORTED, "head_dim must be 128 (got %d)", head_dim);
+    if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1 || top_k < 1 || batch > 65535 || hq > 65535)
+        return fail(MINF_E_ARG, "bad sizes");
+    const int rows_pad = bs_rows_pad(context_size);
+    const int k_eff = top_k < rows_pad ? top_k : rows_pad;
+    if (plan && cap_s < k_eff) return fail(MINF_E_ARG, "cap_s=%d is smaller than top_k=%d", cap_s, k_eff);
+    if ((size_t)rows_pad * 4 > 160 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
+    for (int i = 0; i < 3; ++i)
+        if (q_strides[i] % 4 || k_strides[i] % 4) return fail(MINF_E_ARG, "strides must be multiples of 4 elements");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    PoolArgs p{};
+    p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k);
+    p.q_sb = q_strides[0]; p.q_sh = q_strides[1]; p.q_sn = q_strides[2];
+    p.k_sb = k_strides[0]; p.k_sh = k_strides[1]; p.k_sn = k_strides[2];
+    p.batch = batch; p.hq = hq; p.hkv = hkv; p.n_ctx = context_size; p.rows_pad = rows_pad;
+    p.qpool = static_cast<__nv_bfloat16*>(scratch);
+    p.kpool = p.qpool + (size_t)batch * hq * rows_pad * 128;
+    const long long warps = (long long)batch * (hq + hkv) * rows_pad;
+    bs_pool_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(p);
+    MINF_LAUNCH_OK("bs_pool_kernel");
+
+    BsSelectArgs s{};
+    s.qpool = p.qpool; s.kpool = p.kpool;
+    s.batch = batch; s.hq = hq; s.hkv = hkv; s.n_ctx = context_size;
+    s.rows = (context_size + 63) / 64; s.rows_pad = rows_pad; s.top_k = k_eff;
+    s.head_select = head_select;
+    s.block_index = block_index_out;
+    s.plan = static_cast<unsigned char*>(plan);
+    s.layout = make_plan_layout(context_size, cap_v, cap_s);
+    const size_t smem = (size_t)rows_pad * sizeof(uint32_t);
+    MINF_CUDA_OK(cudaFuncSetAttribute(bs_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bs_select_kernel<<<dim3(rows_pad, hq, batch), 256, smem, st>>>(s);
+    MINF_LAUNCH_OK("bs_select_kernel");
+    return MINF_OK;
+}

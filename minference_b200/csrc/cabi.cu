@@ -6,7 +6,6 @@ char* last_error_buffer() {
     static thread_local char buf[512] = {0};
     return buf;
 }
-extern int g_attn_slots;
 }  // namespace minf
 
 extern "C" const char* minf_version(void) { return "minfer_b200 0.1 (sm_100a)"; }

@@ -20,6 +20,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "common.h"
 #include "plan_layout.h"
 #include "sm100_ptx.cuh"
@@ -601,8 +603,8 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // [batch, heads, tokens, 128] bf16 with element strides (sb, sh, sn); box = 64 x box_rows.
-static int make_tmap(CUtensorMap* tm, const void* base, int batch, int heads, int tokens,
-                     const int64_t st[3], int box_rows, const char* what) {
+int make_tmap_bhnd(CUtensorMap* tm, const void* base, int batch, int heads, int tokens,
+                   const int64_t st[3], int box_rows, const char* what) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(MINF_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     if ((reinterpret_cast<uintptr_t>(base) & 15) || (st[0] % 8) || (st[1] % 8) || (st[2] % 8))
@@ -634,7 +636,14 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     return MINF_OK;
 }
 
-int g_attn_slots = 1;  // tile-sharing width; see minf_set_option
+static int attn_slots() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MINFER_B200_SLOTS");
+        v = (e && e[0] == '2') ? 2 : 1;
+    }
+    return v;
+}
 
 }  // namespace minf
 
@@ -661,9 +670,9 @@ extern "C" int minf_sparse_attention_fwd(
 
     CUtensorMap tq, tk, tv;
     int rc;
-    if ((rc = make_tmap(&tq, q, batch, hq, context_size, q_strides, 128, "q"))) return rc;
-    if ((rc = make_tmap(&tk, k, batch, hkv, context_size, k_strides, 64, "k"))) return rc;
-    if ((rc = make_tmap(&tv, v, batch, hkv, context_size, v_strides, 64, "v"))) return rc;
+    if ((rc = make_tmap_bhnd(&tq, q, batch, hq, context_size, q_strides, 128, "q"))) return rc;
+    if ((rc = make_tmap_bhnd(&tk, k, batch, hkv, context_size, k_strides, 64, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tv, v, batch, hkv, context_size, v_strides, 64, "v"))) return rc;
 
     AttnArgs a{};
     a.o = static_cast<__nv_bfloat16*>(o);
@@ -680,6 +689,6 @@ extern "C" int minf_sparse_attention_fwd(
     a.v_idx = vertical_indexes; a.cap_v = cap_v;
     a.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (g_attn_slots == 2) return launch_attn<2>(tq, tk, tv, a, st);
+    if (attn_slots() == 2) return launch_attn<2>(tq, tk, tv, a, st);
     return launch_attn<1>(tq, tk, tv, a, st);
 }

@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
     const int b = blockIdx.z, h = blockIdx.y;
     const int bh = b * a.heads + h;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (a.nnz_s_per_head && a.nnz_s_per_head[bh] < 0) return;   // head owned by another pattern
     const int nnz_s = a.nnz_s_per_head ? min(a.nnz_s_per_head[bh], a.cap_s) : a.cap_s;
     const int nnz_v = a.nnz_v_per_head ? min(a.nnz_v_per_head[bh], a.cap_v) : a.cap_v;
 
