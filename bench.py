@@ -90,7 +90,7 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------ CPU arm
 
-def cpu_sample(n, hq, hkv, vsize, ssize, seed, budget_s=12.0, max_blocks=24):
+def cpu_sample(n, hq, hkv, vsize, ssize, seed, budget_s=12.0, max_blocks=4096):
     """Time the CPU oracle on a bounded sample of the workload: one head's estimator over the
     full context, its index conversion, and masked-dense attention for a spread of 64-row
     blocks (evaluated until `budget_s` seconds are used).  Returns (TFLOP/s, description)."""

@@ -645,6 +645,22 @@ static int attn_slots() {
     return v;
 }
 
+int launch_sparse_attention_v2(const void* q, const void* k, const void* v, void* o,
+                               const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                               const int64_t o_strides[3], int batch, int hq, int hkv, int context_size,
+                               float sm_scale, const int32_t* head_mode, const int32_t* head_param,
+                               const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
+                               int32_t* status, cudaStream_t st);
+
+static int attn_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MINFER_B200_ATTN");
+        v = (e && e[0] == 'v' && e[1] == '1') ? 1 : 2;
+    }
+    return v;
+}
+
 }  // namespace minf
 
 using namespace minf;
@@ -668,6 +684,10 @@ extern "C" int minf_sparse_attention_fwd(
         return fail(MINF_E_ARG, "o: base and strides must be 16-byte aligned");
     if (cap_v < 0 || cap_s < 1 || cap_v > (1 << 20)) return fail(MINF_E_ARG, "bad plan capacities");
 
+    if (attn_variant() == 2)
+        return launch_sparse_attention_v2(q, k, v, o, q_strides, k_strides, v_strides, o_strides, batch, hq, hkv,
+                                          context_size, sm_scale, head_mode, head_param, plan, vertical_indexes,
+                                          cap_v, cap_s, status, static_cast<cudaStream_t>(stream));
     CUtensorMap tq, tk, tv;
     int rc;
     if ((rc = make_tmap_bhnd(&tq, q, batch, hq, context_size, q_strides, 128, "q"))) return rc;

@@ -1,0 +1,821 @@
+// Sparse flash-attention forward for sm_100a, two query tiles per CTA.
+//
+// One CTA owns 256 consecutive query rows of one head (4 row blocks of 64, the granularity at
+// which the reference defines its index set, ops/pit_sparse_flash_attention_v2.py:64-153) as two
+// 128-row slots.  Warp roles:
+//   warp 0         producer: merges the plans of the four row blocks into one stream of steps.
+//                  A step is 64 or 128 keys -- a contiguous token range (TMA) or gathered
+//                  vertical columns (cp.async) -- with a 128-bit key mask per row block.
+//                  K and V travel through separate rings so a K stage is recycled as soon as
+//                  both QK^T products have read it.
+//   warp 1         issues every tcgen05.mma (lane 0) and owns the TMEM allocation
+//   warps 2-3      spare (they only keep the roles aligned to warpgroups of four)
+//   warps 4-7/8-11 softmax of slot 0 / slot 1, one thread per query row, the whole
+//                  128-key row of S in registers (setmaxnreg moves registers to them)
+// TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written
+// back over the first half of S and feeds the PV product straight from TMEM, so it never
+// touches shared memory.  The two slots alternate: while one slot's softmax runs, the tensor
+// pipe executes the other slot's PV and next QK^T.
+//
+// Semantics kept from the reference kernels: causal mask inside contiguous tiles, none in the
+// gathered-column loop, keys >= context masked, fp32 accumulation, P rounded to bf16,
+// 1/sqrt(d) scale applied with exp2.  A row with no visible key yields zeros.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdlib>
+
+#include "common.h"
+#include "plan_layout.h"
+#include "sm100_ptx.cuh"
+
+namespace minf {
+
+int make_tmap_bhnd(CUtensorMap* tm, const void* base, int batch, int heads, int tokens, const int64_t st[3],
+                   int box_rows, const char* what);   // sparse_attn_fwd.cu
+
+namespace v2 {
+
+constexpr int kNK = 2, kNV = 3, kNM = 8;           // K stages, V stages, step-descriptor ring
+constexpr uint32_t kTile = 128 * 256;              // 128 rows x 128 bf16
+constexpr uint32_t kQOff = 0;
+constexpr uint32_t kKOff = 2 * kTile;
+constexpr uint32_t kVOff = kKOff + kNK * kTile;
+constexpr uint32_t kCtlOff = kVOff + kNV * kTile;
+
+enum StepKind : int { kTileStep = 0, kGatherStep = 1, kEndStep = 2 };
+
+struct Step {
+    int kind;
+    int t;        // first key of a contiguous tile
+    int width;    // 64 or 128 keys
+    int pad;
+    unsigned long long mask[4][2];   // per row block: visible keys (bit i of word w = key 64*w + i)
+};
+
+struct Control {
+    unsigned long long q_full;
+    unsigned long long k_full[kNK], k_empty[kNK], v_full[kNV], v_empty[kNV];
+    unsigned long long m_full[kNM], m_empty[kNM];
+    unsigned long long s_full[2], p_full[2], o_done[2];
+    uint32_t tmem_base;
+    int abort;
+    Step step[kNM];
+    int colring[256];
+};
+
+struct Args {
+    __nv_bfloat16* o;
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    long long o_sb, o_sh, o_sn;
+    long long k_sb, k_sh, k_sn;
+    long long v_sb, v_sh, v_sn;
+    int batch, hq, hkv, n_ctx, rows;
+    float scale_log2;
+    const int32_t* head_mode;
+    const int32_t* head_param;
+    const unsigned char* plan;
+    PlanLayout layout;
+    const int32_t* v_idx;
+    int cap_v;
+    int items_per_head;
+    int32_t* status;
+};
+
+struct Maps {
+    CUtensorMap q, k64, k128, v64, v128;
+};
+
+struct RangeCursor {
+    const int2* rng;
+    int n, ri, base;
+    int2 buf;
+    int a, b;
+    int last_row;
+    __device__ __forceinline__ void fetch(int lane) {
+        if (ri >= n) { a = INT32_MAX; b = INT32_MAX; return; }
+        if (ri - base >= 32 || ri < base) {
+            base = ri;
+            buf = (base + lane < n) ? rng[base + lane] : make_int2(INT32_MAX, INT32_MAX);
+        }
+        a = __shfl_sync(0xffffffffu, buf.x, ri - base);
+        b = __shfl_sync(0xffffffffu, buf.y, ri - base);
+    }
+    __device__ __forceinline__ void init(const int2* r, int count, int last, int lane) {
+        rng = r; n = count; ri = 0; base = -64; last_row = last;
+        fetch(lane);
+    }
+    __device__ __forceinline__ bool live(int n_ctx) const { return ri < n && a <= last_row && a < n_ctx; }
+};
+
+// bits [lo, hi) of a 128-bit mask, 0 <= lo < hi <= 128
+__device__ __forceinline__ void span128(int lo, int hi, unsigned long long& w0, unsigned long long& w1) {
+    auto below = [](int x) -> unsigned long long { return x >= 64 ? ~0ull : (x <= 0 ? 0ull : ((1ull << x) - 1ull)); };
+    w0 |= below(hi) & ~below(lo);
+    w1 |= below(hi - 64) & ~below(lo - 64);
+}
+// keys 0..lim visible (lim may be negative or >= 127)
+__device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigned long long& w1) {
+    auto below = [](int x) -> unsigned long long { return x >= 64 ? ~0ull : (x <= 0 ? 0ull : ((1ull << x) - 1ull)); };
+    w0 = below(lim + 1);
+    w1 = below(lim + 1 - 64);
+}
+
+#ifdef MINF_TIMELINE
+// Debug builds only: cycle stamps of one CTA's roles, read back by a probe script.
+__device__ long long* g_timeline = nullptr;
+__device__ int g_timeline_block = 0;
+#define TL(role, ev, step)                                                                         \
+    do {                                                                                           \
+        if (tl_ptr && tl_n < 2700) {                                                               \
+            tl_ptr[1 + 3 * tl_n] = (ev); tl_ptr[2 + 3 * tl_n] = (step); tl_ptr[3 + 3 * tl_n] = clock64(); \
+            ++tl_n;                                                                                \
+        }                                                                                          \
+    } while (0)
+#define TL_DECL                                                                                    \
+    long long* tl_ptr = (g_timeline && (int)blockIdx.x == g_timeline_block && (threadIdx.x & 31) == 0) \
+                            ? g_timeline + (threadIdx.x >> 5) * 8192 : nullptr;                    \
+    int tl_n = 0;
+#define TL_FLUSH do { if (tl_ptr) tl_ptr[0] = tl_n; } while (0)
+#else
+#define TL(role, ev, step) do { } while (0)
+#define TL_DECL
+#define TL_FLUSH do { } while (0)
+#endif
+
+// One softmax step of one query row: S (fp32, NCH*32 columns at t_s) -> P (bf16 pairs written
+// back over the first NCH*16 columns).  The whole row is held in registers, so TMEM is read
+// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.
+// 2^x on the FMA/ALU pipes (no MUFU): round-to-nearest split x = n + f, |f| <= 1/2, a cubic for
+// 2^f (relative error below 1e-3, well under the bf16 rounding of P) and n added to the
+// exponent field.  x must be finite; values below -126 are clamped (2^-126 instead of 0).
+__device__ __forceinline__ float exp2_fma(float x) {
+    x = fmaxf(x, -126.f);
+    const float t = x + 12582912.f;              // 1.5 * 2^23: the integer part lands in the mantissa
+    const float f = x - (t - 12582912.f);
+    float p = fmaf(f, 0.0555041f, 0.2402265f);
+    p = fmaf(p, f, 0.6931472f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+template <int NCH, int SV>
+__device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
+                                            float scale_log2, bool have_o, float& m_ref, float& l_sum) {
+    uint32_t sr[NCH][32];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
+    tmem_wait_ld();
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        if (cm != 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+    }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+    float alpha = 1.f;
+    if (mx > m_ref + 8.f) {          // raise the reference maximum only on a jump of more than 2^8
+        alpha = fast_exp2(m_ref - mx);
+        l_sum *= alpha;
+        m_ref = mx;
+    }
+    const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+    // O of this slot is stable here: the QK^T that filled S was issued after the previous PV
+    if (have_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            tmem_ld32(t_o + 32 * c, orow);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+            tmem_st32(t_o + 32 * c, orow);
+        }
+    }
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        const bool dense = cm == 0xffffffffu;    // masked keys are -inf and must give exactly 0: MUFU only
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float x0 = fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m);
+            const float x1 = fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m);
+            float p0, p1;
+            if (dense && ((SV == 2 && (i & 6) == 6) || (SV == 3 && (i & 2) == 2))) {   // a share of the pairs goes to the FMA pipe
+                p0 = exp2_fma(x0);
+                p1 = exp2_fma(x1);
+            } else if ((SV == 4 && (i & 2)) || SV == 5) {    // TIMING PROBE ONLY: no exponential
+                p0 = x0 * 1e-3f;
+                p1 = x1 * 1e-3f;
+            } else {
+                p0 = fast_exp2(x0);
+                p1 = fast_exp2(x1);
+            }
+            ps4[(i >> 1) & 3] += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s + 16 * c, pk);
+    }
+    l_sum += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+    tmem_wait_st();
+}
+
+// Same step with the row streamed through registers 32 keys at a time (two reads of S).
+__device__ __forceinline__ void softmax_row_chunked(int nchunks, uint32_t t_s, uint32_t t_o, unsigned long long m0,
+                                                    unsigned long long m1, float scale_log2, bool have_o,
+                                                    float& m_ref, float& l_sum) {
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+    for (int c = 0; c < nchunks; ++c) {
+        uint32_t sr[32];
+        tmem_ld32(t_s + 32 * c, sr);
+        tmem_wait_ld();
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        if (cm == 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[i]));
+        } else if (cm != 0u) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                mx4[i & 3] = fmaxf(mx4[i & 3], ((cm >> i) & 1u) ? __uint_as_float(sr[i]) : -INFINITY);
+        }
+    }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+    float alpha = 1.f;
+    if (mx > m_ref + 8.f) {
+        alpha = fast_exp2(m_ref - mx);
+        l_sum *= alpha;
+        m_ref = mx;
+    }
+    const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+    if (have_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            tmem_ld32(t_o + 32 * c, orow);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+            tmem_st32(t_o + 32 * c, orow);
+        }
+    }
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int c = 0; c < nchunks; ++c) {
+        uint32_t sr[32];
+        tmem_ld32(t_s + 32 * c, sr);
+        tmem_wait_ld();
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), scale_log2, neg_m));
+            float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), scale_log2, neg_m));
+            if (cm != 0xffffffffu) {
+                p0 = ((cm >> i) & 1u) ? p0 : 0.f;
+                p1 = ((cm >> (i + 1)) & 1u) ? p1 : 0.f;
+            }
+            ps4[(i >> 1) & 3] += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s + 16 * c, pk);
+    }
+    l_sum += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+    tmem_wait_st();
+}
+
+template <int SV>
+__global__ void __launch_bounds__(384, 1)
+sparse_attn_fwd_v2_kernel(const __grid_constant__ Maps tm, const Args a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    Control* ctl = reinterpret_cast<Control*>(smem + kCtlOff);
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TL_DECL
+
+    const int bh_count = a.batch * a.hq;
+    const int item = a.items_per_head - 1 - (int)(blockIdx.x / bh_count);   // latest rows (most work) first
+    const int bh = (int)(blockIdx.x % bh_count);
+    const int b = bh / a.hq, h = bh % a.hq;
+    const int hk = h / (a.hq / a.hkv);
+    const int rb0 = item * 4;
+    const int row0 = rb0 * 64;
+
+    if (__syncthreads_or(threadIdx.x == 0 && *(volatile int32_t*)(a.status + MINF_ST_ERROR) != 0)) return;
+    if ((smem_base & 1023u) != 0u) {
+        if (threadIdx.x == 0) atomicOr(a.status + MINF_ST_ERROR, 2);
+        return;
+    }
+    const int mode = a.head_mode ? a.head_mode[h] : MINF_MODE_PLAN;
+    const int n_init = mode == MINF_MODE_ASHAPE ? a.head_param[2 * h] : 0;
+    const int n_local = mode == MINF_MODE_ASHAPE ? a.head_param[2 * h + 1] : 0;
+
+    auto bar = [&](const unsigned long long* p) { return smem_u32(p); };
+    volatile int* abort_flag = &ctl->abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(&ctl->q_full), 1);
+        for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 1); mbar_init(bar(&ctl->k_empty[s]), 1); }
+        for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 1); mbar_init(bar(&ctl->v_empty[s]), 1); }
+        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA thread + 8 softmax warps
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(&ctl->s_full[s]), 1);
+            mbar_init(bar(&ctl->p_full[s]), 128);
+            mbar_init(bar(&ctl->o_done[s]), 1);
+        }
+        ctl->abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl->tmem_base;
+
+    // Warpgroup 0 (producer, MMA issuer, two spare warps) needs few registers; the two softmax
+    // warpgroups hold a whole 128-key row of S per thread.
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        if (lane == 0) {
+            tma_prefetch_desc(&tm.q); tma_prefetch_desc(&tm.k64); tma_prefetch_desc(&tm.k128);
+            tma_prefetch_desc(&tm.v64); tma_prefetch_desc(&tm.v128);
+            mbar_arrive_expect_tx(bar(&ctl->q_full), 2 * kTile);
+            for (int s = 0; s < 2; ++s) {
+                tma_load_4d(smem_base + kQOff + s * kTile, &tm.q, bar(&ctl->q_full), 0, row0 + 128 * s, h, b);
+                tma_load_4d(smem_base + kQOff + s * kTile + 16384, &tm.q, bar(&ctl->q_full), 64, row0 + 128 * s, h, b);
+            }
+        }
+        int step = 0;
+        bool ok = true;
+        auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
+            const int s = idx % ring, use = idx / ring;
+            if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
+            return true;
+        };
+        // publish the descriptor of `step` (written by lane 0 from the arguments)
+        auto publish = [&](int kind, int t, int width, const unsigned long long (&mk)[4][2]) -> bool {
+            if (!wait_use(ctl->m_empty, kNM, step)) return false;
+            if (lane == 0) {
+                Step& st = ctl->step[step % kNM];
+                st.kind = kind; st.t = t; st.width = width;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
+                mbar_arrive(bar(&ctl->m_full[step % kNM]));
+            }
+            return true;
+        };
+        auto load_tile = [&](int t, int width) -> bool {
+            if (!wait_use(ctl->k_empty, kNK, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                tma_load_4d(dst, m, fb, 0, t, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, t, hk, b);
+            }
+            if (!wait_use(ctl->v_empty, kNV, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                tma_load_4d(dst, m, fb, 0, t, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, t, hk, b);
+            }
+            return true;
+        };
+
+        if (mode == MINF_MODE_ASHAPE) {
+            const int r_hi = min(row0 + 256, a.n_ctx) - 1;
+            int w0 = row0 - n_local + 1;
+            w0 = w0 < 0 ? 0 : (w0 & ~63);
+            const bool sinks = a.n_ctx > n_local && r_hi >= n_local;
+            const int sink_end = sinks ? min(min(n_init, w0), a.n_ctx) : 0;
+            unsigned long long all[4][2];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) { all[r][0] = ~0ull; all[r][1] = ~0ull; }
+            for (int phase = 0; phase < 2 && ok; ++phase) {
+                const int t_lo = phase == 0 ? 0 : w0;
+                const int t_hi = phase == 0 ? sink_end : r_hi + 1;
+                for (int t = t_lo; t < t_hi && ok;) {
+                    const int width = (t_hi - t > 64) ? 128 : 64;
+                    if (!publish(kTileStep, t, width, all)) break;
+                    if (!load_tile(t, width)) break;
+                    ++step;
+                    t += width;
+                }
+            }
+        } else {
+            const unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
+            const int32_t* rng_cnt = reinterpret_cast<const int32_t*>(slot);
+            const int2* rng_all = reinterpret_cast<const int2*>(slot + a.layout.rng_off);
+            RangeCursor cur[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int m = rb0 + r;
+                const bool present = m < a.rows;
+                cur[r].init(present ? rng_all + plan_rng_index(m, a.layout.cap_s) : nullptr,
+                            present ? rng_cnt[m] : 0, m * 64 + 63, lane);
+            }
+            while (ok) {
+                int t = INT32_MAX;
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (cur[r].live(a.n_ctx)) t = min(t, cur[r].a);
+                if (t == INT32_MAX) break;
+                unsigned long long mk[4][2];
+                unsigned long long any_hi = 0ull;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    mk[r][0] = 0ull; mk[r][1] = 0ull;
+                    while (cur[r].live(a.n_ctx) && cur[r].a < t + 128) {
+                        const int hi = min(cur[r].b, t + 128);
+                        span128(cur[r].a - t, hi - t, mk[r][0], mk[r][1]);
+                        if (cur[r].b <= t + 128) { ++cur[r].ri; cur[r].fetch(lane); }
+                        else { cur[r].a = t + 128; break; }
+                    }
+                    any_hi |= mk[r][1];
+                }
+                const int width = any_hi ? 128 : 64;
+                if (!publish(kTileStep, t, width, mk)) break;
+                TL(0, 1, step);
+                if (!load_tile(t, width)) break;
+                TL(0, 2, step);
+                ++step;
+            }
+            // ---- gathered columns
+            const int words = a.layout.words_v;
+            const uint32_t* bits = reinterpret_cast<const uint32_t*>(slot + a.layout.bits_off);
+            const int32_t* vlist = a.v_idx ? a.v_idx + (size_t)bh * a.cap_v : nullptr;
+            int filled = 0, emitted = 0;
+            auto flush_chunk = [&](int count) {   // count <= 128
+                const int width = count > 64 ? 128 : 64;
+                int e[4];
+                bool val[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    val[q4] = lane + 32 * q4 < count;
+                    e[q4] = ctl->colring[(emitted + 32 * q4 + lane) & 255];
+                }
+                unsigned long long mk[4][2];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    unsigned bl[4];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) bl[q4] = __ballot_sync(0xffffffffu, val[q4] && ((e[q4] >> (28 + r)) & 1));
+                    mk[r][0] = (unsigned long long)bl[0] | ((unsigned long long)bl[1] << 32);
+                    mk[r][1] = (unsigned long long)bl[2] | ((unsigned long long)bl[3] << 32);
+                }
+                if (!publish(kGatherStep, 0, width, mk)) return;
+                int col[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) col[q4] = val[q4] ? (e[q4] & 0x0fffffff) : 0;
+                const int chunk = lane & 15, sub = lane >> 4;
+                const int iters = width / 2;
+                // K rows
+                if (!wait_use(ctl->k_empty, kNK, step)) return;
+                {
+                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                    const __nv_bfloat16* kb = a.k + b * a.k_sb + hk * a.k_sh;
+#pragma unroll 4
+                    for (int it = 0; it < iters; ++it) {
+                        const int r = 2 * it + sub;
+                        const int src_lane = r & 31, q4 = r >> 5;
+                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
+                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
+                        cp_async_16(dst + off, kb + (long long)c * a.k_sn + chunk * 8);
+                    }
+                    cp_async_commit();
+                }
+                if (!wait_use(ctl->v_empty, kNV, step)) { cp_async_wait<0>(); return; }
+                {
+                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                    const __nv_bfloat16* vb = a.v + b * a.v_sb + hk * a.v_sh;
+#pragma unroll 4
+                    for (int it = 0; it < iters; ++it) {
+                        const int r = 2 * it + sub;
+                        const int src_lane = r & 31, q4 = r >> 5;
+                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
+                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
+                        cp_async_16(dst + off, vb + (long long)c * a.v_sn + chunk * 8);
+                    }
+                    cp_async_commit();
+                }
+                cp_async_wait<1>();            // K rows landed
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(&ctl->k_full[step % kNK]));
+                cp_async_wait<0>();            // V rows landed
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(&ctl->v_full[step % kNV]));
+                emitted += count;
+                ++step;
+            };
+            for (int w = 0; w < words && ok; ++w) {
+                uint32_t wr[4];
+                uint32_t any = 0;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int m = rb0 + r;
+                    wr[r] = m < a.rows ? bits[(size_t)m * words + w] : 0u;
+                    any |= wr[r];
+                }
+                if (any == 0u) continue;
+                const bool mine = (any >> lane) & 1u;
+                const int pos = filled + __popc(any & ((1u << lane) - 1u));
+                if (mine) {
+                    int e = vlist[32 * w + lane] & 0x0fffffff;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) e |= (int)((wr[r] >> lane) & 1u) << (28 + r);
+                    ctl->colring[pos & 255] = e;
+                }
+                filled += __popc(any);
+                __syncwarp();
+                if (filled - emitted >= 128) flush_chunk(128);
+            }
+            if (ok && filled > emitted) flush_chunk(filled - emitted);
+        }
+        if (ok) {
+            unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
+            publish(kEndStep, 0, 0, none);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        {   // every lane follows the control flow (so addresses stay warp-uniform), lane 0 issues
+            const bool issuer = lane == 0;
+            bool ok = mbar_wait(bar(&ctl->q_full), 0, abort_flag);
+            // descriptors are read straight from the shared-memory ring; a slot of the ring is
+            // handed back to the producer only when both query slots are past its step
+            auto kind_of = [&](int j) { return ctl->step[j % kNM].kind; };
+            auto width_of = [&](int j) { return ctl->step[j % kNM].width; };
+            auto part_of = [&](int j, int s) {
+                const Step& st = ctl->step[j % kNM];
+                return (st.mask[2 * s][0] | st.mask[2 * s][1] | st.mask[2 * s + 1][0] | st.mask[2 * s + 1][1]) != 0ull;
+            };
+            // Descriptor words: the high word (stride offset 1024 B, version, 128-byte swizzle) is
+            // a constant, the low word is (address >> 4) | (leading offset >> 4) << 16, so walking
+            // along K is an integer add of a compile-time constant.
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+            const uint32_t q_lo[2] = {((smem_base + kQOff) >> 4) | (1u << 16), ((smem_base + kQOff + kTile) >> 4) | (1u << 16)};
+            auto issue_s = [&](int j, int slot, int width) {
+                const uint32_t idesc = width == 128 ? umma_idesc(128, 128, true, false, false)
+                                                    : umma_idesc(128, 64, true, false, false);
+                const uint32_t d = tmem + slot * 256 + 128;
+                const uint32_t a_lo = q_lo[slot];
+                const uint32_t b_lo = ((smem_base + kKOff + (j % kNK) * kTile) >> 4) | (1u << 16);
+                if (issuer) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
+                        umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
+                    }
+                    umma_commit(bar(&ctl->s_full[slot]));
+                }
+            };
+            int npv[2] = {0, 0};
+            auto issue_pv = [&](int j, int slot, int width) {
+                constexpr uint32_t idesc = umma_idesc(128, 128, true, false, true);
+                const uint32_t d = tmem + slot * 256;
+                const uint32_t p = tmem + slot * 256 + 128;
+                const uint32_t b_lo = ((smem_base + kVOff + (j % kNV) * kTile) >> 4) | ((16384u >> 4) << 16);
+                const uint32_t acc0 = npv[slot] > 0 ? 1u : 0u;
+                if (issuer) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, kk > 0 ? 1u : acc0);
+                    if (width == 128) {
+#pragma unroll
+                        for (int kk = 4; kk < 8; ++kk)
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, 1u);
+                    }
+                }
+                ++npv[slot];
+            };
+
+            // Steps are issued in order, slot 0 then slot 1: PV(s, j) as soon as P(s, j) is ready,
+            // followed at once by QK^T(s, j+1) so that the slot's next softmax can start while
+            // the other slot's products run.  Waits are blocking (the hardware suspends the
+            // thread), which keeps this warp out of the issue slots of the softmax warps.
+            auto wait_step = [&](int j) { if (ok) ok = mbar_wait(bar(&ctl->m_full[j % kNM]), (j / kNM) & 1, abort_flag); };
+            int j = 0;
+            wait_step(0);
+            if (ok && kind_of(0) != kEndStep) {
+                ok = mbar_wait(bar(&ctl->k_full[0]), 0, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    for (int s = 0; s < 2; ++s)
+                        if (part_of(0, s)) issue_s(0, s, width_of(0));
+                    if (issuer) umma_commit(bar(&ctl->k_empty[0]));
+                }
+            }
+            while (ok && kind_of(j) != kEndStep) {
+                wait_step(j + 1);
+                if (!ok) break;
+                const bool nxt_live = kind_of(j + 1) != kEndStep;
+                ok = mbar_wait(bar(&ctl->v_full[j % kNV]), (j / kNV) & 1, abort_flag);
+                bool k_ready = false;
+                for (int s = 0; s < 2 && ok; ++s) {
+                    if (part_of(j, s)) {
+                        ok = mbar_wait(bar(&ctl->p_full[s]), npv[s] & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        TL(1, 10 + s, j);
+                        issue_pv(j, s, width_of(j));
+                        TL(1, 12 + s, j);
+                    }
+                    if (nxt_live && part_of(j + 1, s)) {
+                        if (!k_ready) { ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag); k_ready = true; }
+                        if (!ok) break;
+                        tc_fence_after();
+                        TL(1, 20 + s, j + 1);
+                        issue_s(j + 1, s, width_of(j + 1));
+                        TL(1, 22 + s, j + 1);
+                    }
+                }
+                if (!ok) break;
+                if (nxt_live && !k_ready) ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag);
+                if (!ok) break;
+                if (issuer) {
+                    umma_commit(bar(&ctl->v_empty[j % kNV]));
+                    if (nxt_live) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
+                    mbar_arrive(bar(&ctl->m_empty[j % kNM]));
+                }
+                ++j;
+            }
+            if (ok && issuer) mbar_arrive(bar(&ctl->m_empty[j % kNM]));   // the end marker itself
+            if (ok && issuer) {
+                umma_commit(bar(&ctl->o_done[0]));
+                umma_commit(bar(&ctl->o_done[1]));
+            }
+        }
+    } else if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    } else {
+        // ------------------------------------------------------------------ softmax / epilogue
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int slot = (warp - 4) >> 2;
+        const int sub = warp & 3;
+        const int row_local = 32 * sub + lane;
+        const int rb_local = 2 * slot + (row_local >> 6);
+        const int row = row0 + 128 * slot + row_local;
+        const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+        const uint32_t t_o = tmem + slot * 256 + lane_base;
+        const uint32_t t_s = t_o + 128;
+
+        float m_ref = -INFINITY, l_sum = 0.f;
+        int n = 0;
+        bool ok = true;
+        for (int j = 0; ok; ++j) {
+            ok = mbar_wait(bar(&ctl->m_full[j % kNM]), (j / kNM) & 1, abort_flag);
+            if (!ok) break;
+            const Step& st = ctl->step[j % kNM];
+            const int kind = st.kind;
+            const int t = st.t, width = st.width;
+            unsigned long long m0 = st.mask[rb_local][0], m1 = st.mask[rb_local][1];
+            const bool slot_in = (st.mask[2 * slot][0] | st.mask[2 * slot][1] | st.mask[2 * slot + 1][0] | st.mask[2 * slot + 1][1]) != 0ull;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(&ctl->m_empty[j % kNM]));
+            if (kind == kEndStep) break;
+            if (!slot_in) continue;
+
+            if (kind == kTileStep) {
+                unsigned long long c0, c1;
+                upto128(min(row - t, a.n_ctx - 1 - t), c0, c1);      // causal and inside the context
+                if (mode == MINF_MODE_ASHAPE) {
+                    unsigned long long lo0, lo1, s0, s1;
+                    upto128(row - n_local - t, lo0, lo1);             // keys at distance >= n_local ...
+                    upto128(n_init - 1 - t, s0, s1);                  // ... are only visible as sinks
+                    m0 = c0 & (~lo0 | s0);
+                    m1 = c1 & (~lo1 | s1);
+                } else {
+                    m0 &= c0; m1 &= c1;
+                }
+            }
+            if (row >= a.n_ctx) { m0 = 0ull; m1 = 0ull; }
+            ok = mbar_wait(bar(&ctl->s_full[slot]), n & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            TL(2 + slot, 1, j);
+            if (SV == 0) softmax_row_chunked(width >> 5, t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
+            else if (width == 128) softmax_row<4, SV>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
+            else softmax_row<2, SV>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
+            tc_fence_before();
+            mbar_arrive(bar(&ctl->p_full[slot]));
+            TL(2 + slot, 2, j);
+            ++n;
+        }
+
+        // epilogue: TMEM loads are warp-collective, so the whole warp runs them
+        bool warp_ok = __all_sync(0xffffffffu, ok);
+        if (warp_ok) {
+            const bool w = mbar_wait(bar(&ctl->o_done[slot]), 0, abort_flag);
+            warp_ok = __all_sync(0xffffffffu, w);
+        }
+        if (warp_ok) {
+            tc_fence_after();
+            const float inv = (n > 0 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
+            __nv_bfloat16* dst = a.o + b * a.o_sb + h * a.o_sh + (long long)row * a.o_sn;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t orow[32];
+                if (n > 0) {
+                    tmem_ld32(t_o + 32 * c, orow);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) orow[i] = 0u;
+                }
+                if (row < a.n_ctx) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 out;
+                        out.x = pack_bf16x2(__uint_as_float(orow[8 * q4 + 0]) * inv, __uint_as_float(orow[8 * q4 + 1]) * inv);
+                        out.y = pack_bf16x2(__uint_as_float(orow[8 * q4 + 2]) * inv, __uint_as_float(orow[8 * q4 + 3]) * inv);
+                        out.z = pack_bf16x2(__uint_as_float(orow[8 * q4 + 4]) * inv, __uint_as_float(orow[8 * q4 + 5]) * inv);
+                        out.w = pack_bf16x2(__uint_as_float(orow[8 * q4 + 6]) * inv, __uint_as_float(orow[8 * q4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = out;
+                    }
+                }
+            }
+        }
+    }
+
+    TL_FLUSH;
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && ctl->abort) atomicOr(a.status + MINF_ST_ERROR, 1);
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace v2
+
+#ifdef MINF_TIMELINE
+extern "C" int minf_debug_timeline(long long* buf, int block) {
+    cudaMemcpyToSymbol(v2::g_timeline, &buf, sizeof(buf));
+    cudaMemcpyToSymbol(v2::g_timeline_block, &block, sizeof(block));
+    return 0;
+}
+#endif
+
+int launch_sparse_attention_v2(const void* q, const void* k, const void* v, void* o,
+                               const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                               const int64_t o_strides[3], int batch, int hq, int hkv, int context_size,
+                               float sm_scale, const int32_t* head_mode, const int32_t* head_param,
+                               const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
+                               int32_t* status, cudaStream_t st) {
+    v2::Maps tm;
+    int rc;
+    if ((rc = make_tmap_bhnd(&tm.q, q, batch, hq, context_size, q_strides, 128, "q"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.k64, k, batch, hkv, context_size, k_strides, 64, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.k128, k, batch, hkv, context_size, k_strides, 128, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.v64, v, batch, hkv, context_size, v_strides, 64, "v"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.v128, v, batch, hkv, context_size, v_strides, 128, "v"))) return rc;
+    v2::Args a{};
+    a.o = static_cast<__nv_bfloat16*>(o);
+    a.k = static_cast<const __nv_bfloat16*>(k);
+    a.v = static_cast<const __nv_bfloat16*>(v);
+    a.o_sb = o_strides[0]; a.o_sh = o_strides[1]; a.o_sn = o_strides[2];
+    a.k_sb = k_strides[0]; a.k_sh = k_strides[1]; a.k_sn = k_strides[2];
+    a.v_sb = v_strides[0]; a.v_sh = v_strides[1]; a.v_sn = v_strides[2];
+    a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size; a.rows = (context_size + 63) / 64;
+    a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.head_mode = head_mode; a.head_param = head_param;
+    a.plan = static_cast<const unsigned char*>(plan);
+    a.layout = make_plan_layout(context_size, cap_v, cap_s);
+    a.v_idx = vertical_indexes; a.cap_v = cap_v;
+    a.status = status;
+    a.items_per_head = (a.rows + 3) / 4;
+    const size_t smem = v2::kCtlOff + sizeof(v2::Control);
+    const long long ctas = (long long)a.items_per_head * batch * hq;
+    if (ctas > 0x7fffffffLL) return fail(MINF_E_UNSUPPORTED, "grid too large");
+    static int sv = -1;
+    if (sv < 0) { const char* e = getenv("MINFER_B200_SV"); sv = e ? atoi(e) : 1; }
+#define MINF_LAUNCH_SV(N)                                                                                          \
+    do {                                                                                                           \
+        MINF_CUDA_OK(cudaFuncSetAttribute(v2::sparse_attn_fwd_v2_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        v2::sparse_attn_fwd_v2_kernel<N><<<(unsigned)ctas, 384, smem, st>>>(tm, a);                                \
+    } while (0)
+    if (sv == 1) MINF_LAUNCH_SV(1); else if (sv == 2) MINF_LAUNCH_SV(2); else if (sv == 3) MINF_LAUNCH_SV(3);
+    else if (sv == 4) MINF_LAUNCH_SV(4); else if (sv == 5) MINF_LAUNCH_SV(5); else MINF_LAUNCH_SV(0);
+    MINF_LAUNCH_OK("sparse_attn_fwd_v2_kernel");
+    return MINF_OK;
+}
+
+}  // namespace minf
