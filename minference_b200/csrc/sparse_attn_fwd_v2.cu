@@ -413,7 +413,18 @@ sparse_attn_fwd_v2_kernel(const __grid_constant__ Maps tm, const Args a) {
                 const int t_hi = phase == 0 ? sink_end : r_hi + 1;
                 for (int t = t_lo; t < t_hi && ok;) {
                     const int width = (t_hi - t > 64) ? 128 : 64;
-                    if (!publish(kTileStep, t, width, all)) break;
+                    // a row block takes part only if one of its rows can see a key of the tile:
+                    // the tile starts at or before its last row and reaches its window (or is a sink tile)
+                    unsigned long long mk[4][2];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int first = (rb0 + r) * 64, last = first + 63;
+                        const bool sees = last >= t && (phase == 0 || t + width - 1 >= first - n_local + 1 ||
+                                                        (a.n_ctx > n_local && t < n_init));   // window tile that also holds sinks
+                        mk[r][0] = sees ? all[r][0] : 0ull;
+                        mk[r][1] = sees ? all[r][1] : 0ull;
+                    }
+                    if (!publish(kTileStep, t, width, mk)) break;
                     if (!load_tile(t, width)) break;
                     ++step;
                     t += width;

@@ -1,0 +1,83 @@
+"""The patch / configuration API that mirrors the reference's MInference(...)(model)."""
+import json
+
+import pytest
+import torch
+
+
+def test_config_mirrors_reference_fields(tmp_path):
+    from minference_b200 import MInferenceConfig
+    from minference_b200.configs.model2path import register_model, get_support_models, synthetic_pattern_table, save_pattern_table
+
+    table = synthetic_pattern_table(2, 4, seed=3, mix=("vertical_and_slash", "stream_llm", "block_sparse"))
+    assert len(table) == 2 and set(table[0]) == {"0", "1", "2", "3"}
+    for entry in table[0].values():
+        assert entry[0] in ("vertical_and_slash", "stream_llm", "block_sparse") and len(entry) == 4
+    path = tmp_path / "pattern.json"
+    save_pattern_table(table, str(path))
+    assert json.load(open(path)) == table
+    cfg = MInferenceConfig(attn_type="minference", config_path=str(path), starting_layer=1)
+    assert cfg.config_path == str(path) and cfg.attn_kwargs["starting_layer"] == 1 and cfg.kv_type == "dense"
+    assert "minference" in MInferenceConfig.get_available_attn_types()
+    register_model("unit/test-model", str(path))
+    assert "unit/test-model" in get_support_models()
+    assert MInferenceConfig(attn_type="minference", model_name="unit/test-model").config_path == str(path)
+    with pytest.raises(ValueError):
+        MInferenceConfig(attn_type="minference", model_name="no/such-model")
+    with pytest.raises(ValueError):
+        MInferenceConfig(attn_type="inf_llm")
+    with pytest.raises(ValueError):
+        MInferenceConfig(kv_type="snapkv", config_path=str(path))
+
+
+def test_layer_pattern_parsing():
+    from minference_b200 import _cabi
+    from minference_b200.modules.minference_forward import LayerPattern, clamp_budgets
+
+    assert clamp_budgets(8192, 1000, 6096) == (1000, 6096)
+    assert clamp_budgets(100, 1000, 6096) == (100, 100)
+    assert clamp_budgets(8192, 5, 5) == (30, 50)
+    layer = {"0": ["vertical_and_slash", 30, 800, 1], "1": ["stream_llm", 128, 512, 1], "2": ["block_sparse", 0, 0, 1]}
+    pat = LayerPattern(layer, 4, 8192, None, "cpu")        # head 3 falls back to the default pattern
+    assert pat.head_mode.tolist() == [_cabi.MODE_PLAN, _cabi.MODE_ASHAPE, _cabi.MODE_PLAN, _cabi.MODE_PLAN]
+    assert pat.head_param.tolist()[1] == [128, 512]
+    assert pat.vertical_size.tolist() == [30, -1, -1, 1000] and pat.slash_size.tolist() == [800, -1, -1, 6096]
+    assert pat.block_select.tolist() == [0, 0, 1, 0]
+    assert pat.cap_v == 1000 and pat.cap_s == 6096 and pat.any_vs and pat.any_bs
+    half = LayerPattern(layer, 4, 8192, 0.5, "cpu")        # minference_ratio scales the budgets
+    assert half.vertical_size.tolist()[3] == 500 and half.slash_size.tolist()[3] == 3048
+
+
+@pytest.mark.gpu
+def test_patched_llama_matches_dense_when_budgets_cover_everything(tmp_path):
+    """With vertical/slash budgets >= the sequence the sparse pattern is the full causal mask, so a
+    patched random-init Llama must reproduce the stock attention's logits."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from minference_b200 import MInference
+    from minference_b200.configs.model2path import save_pattern_table, synthetic_pattern_table
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=1000, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=4096,
+                      rope_theta=5e5, attn_implementation="sdpa")
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 1000, (1, 700), device="cuda")
+    with torch.no_grad():
+        ref = model(ids, use_cache=False).logits.float()
+    path = tmp_path / "full.json"
+    save_pattern_table(synthetic_pattern_table(2, 4, vertical=4096, slash=4096), str(path))
+    model = MInference("minference", config_path=str(path))(model)
+    with torch.no_grad():
+        out = model(ids, use_cache=False).logits.float()
+    assert torch.isfinite(out).all()
+    assert (out - ref).abs().max().item() < 0.15 and (out - ref).abs().mean().item() < 0.02
+    # a sparse table runs too and stays close on this short input
+    save_pattern_table(synthetic_pattern_table(2, 4, seed=1, mix=("vertical_and_slash", "stream_llm", "block_sparse"),
+                                               vertical=100, slash=300, n_init=64, n_local=256), str(path))
+    model = MInference("minference", config_path=str(path))(model)
+    with torch.no_grad():
+        out2 = model(ids, use_cache=False).logits.float()
+    assert torch.isfinite(out2).all()
