@@ -121,6 +121,29 @@ int minf_vs_estimate(
     void* scratch, int32_t* status, void* stream);
 
 /*
+ * minf_vs_estimate for callers that cannot provide scratch memory and must not trigger an
+ * allocation (a plugin inside a process whose device memory is a pre-carved arena it has no
+ * handle to, or a caller on a path where allocators are off limits).  No counterpart in the
+ * reference.  Same inputs and outputs as minf_vs_estimate minus `scratch` and the optional score
+ * outputs; the scratch is a fixed 16 MiB array in the library's device image (one per GPU that
+ * loads the library, held until the process exits), which limits the problem to about
+ * batch*hq*context_size <= 1M (minf_vs_estimate_scratch_bytes() must not exceed
+ * minf_vs_estimate_static_scratch_limit()); larger problems return MINF_E_UNSUPPORTED.
+ * Nothing is allocated or freed.  All calls on a GPU share the array: calls that may overlap on
+ * the device race with each other and must be serialised by the caller.  The first call on a
+ * device looks up the array's device address once; make that call outside any stream capture.
+ */
+size_t minf_vs_estimate_static_scratch_limit(void);
+int minf_vs_estimate_static(
+    const void* q, const void* k,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim,
+    const int32_t* vertical_size, const int32_t* slash_size,
+    int cap_v, int cap_s,
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
+    int32_t* status, void* stream);
+
+/*
  * Sparse flash-attention forward for all heads in one launch.  Replaces
  * _triton_mixed_sparse_attention (ops/pit_sparse_flash_attention_v2.py:48-192),
  * _triton_block_sparse_attention (ops/block_sparse_flash_attention.py:29-148) and the

@@ -36,6 +36,9 @@ SIGNATURES = {
     "minf_vs_estimate_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_estimate": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
                          [c_int, c_int] + [c_void_p] * 6 + [c_void_p, c_void_p, c_void_p]),
+    "minf_vs_estimate_static_scratch_limit": (c_size_t, []),
+    "minf_vs_estimate_static": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
+                                [c_int, c_int] + [c_void_p] * 4 + [c_void_p, c_void_p]),
     "minf_sparse_attention_fwd": (c_int, [c_void_p] * 4 + [_I64x3] * 4 + [c_int] * 5 + [c_float] +
                                   [c_void_p] * 4 + [c_int, c_int] + [c_void_p, c_void_p]),
     "minf_plan_count_tiles": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p]),

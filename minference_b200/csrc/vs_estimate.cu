@@ -468,3 +468,75 @@ extern "C" int minf_vs_estimate(
     MINF_LAUNCH_OK("vs_select_kernel");
     return MINF_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of the estimator.
+//
+// Some hosts of this library cannot hand it scratch memory: an attention plugin loaded into
+// a serving process whose device memory is one arena carved up at start-up (the plugin has no
+// handle to that allocator and the process may have no free device memory left to cudaMalloc
+// from), or a caller on a latency-critical path that is not allowed to touch an allocator at
+// all.  For them the scratch of the estimator lives in the library image: a fixed array in
+// device global memory that exists once per GPU that has loaded the library, from the moment
+// the module is loaded until the process ends.
+//
+// The array's name is only meaningful to device code.  Host code must ask the runtime where the
+// array lives on the current device (cudaGetSymbolAddress); handing the bare symbol to a kernel
+// would pass a host-side placeholder, not a device address.  The lookup is done once per device,
+// on the first call made with that device current, and cached.
+namespace minf {
+
+constexpr size_t kStaticScratchBytes = 16u << 20;    // 16 MiB per GPU, stated in the header as the limit
+static __device__ __align__(256) unsigned char g_estimate_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_estimate_scratch_addr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch on the current device (looked up on first use).
+static int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    MINF_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MINF_E_UNSUPPORTED, "device ordinal %d out of range", dev);
+    void* p = __atomic_load_n(&g_estimate_scratch_addr[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        MINF_CUDA_OK(cudaGetSymbolAddress(&p, g_estimate_scratch));
+        if (!p) return fail(MINF_E_CUDA, "cudaGetSymbolAddress returned a null address");
+        __atomic_store_n(&g_estimate_scratch_addr[dev], p, __ATOMIC_RELEASE);   // same value from every thread
+    }
+    *out = p;
+    return MINF_OK;
+}
+
+}  // namespace minf
+
+extern "C" size_t minf_vs_estimate_static_scratch_limit(void) { return minf::kStaticScratchBytes; }
+
+// Same computation and outputs as minf_vs_estimate, without a caller-provided scratch buffer and
+// without any allocation (no cudaMalloc/cudaFree, no allocating library call): the scratch is the
+// static array above.  Problems larger than the array are refused.  The array is shared by every
+// call on the GPU and still holds what the previous call left there; the parts that must start
+// at zero (the diagonal-score accumulators) are cleared on the stream before the kernels run, as in
+// the buffer-taking entry point.  Two calls whose kernels may overlap on the same GPU (different
+// streams, or different host threads) would use the same scratch at once: that is a data race the
+// caller must exclude.  The first call on a device performs the one-time address lookup and
+// should therefore be made outside any stream capture.
+extern "C" int minf_vs_estimate_static(
+    const void* q, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim,
+    const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
+    int32_t* status, void* stream) {
+    const size_t need = minf_vs_estimate_scratch_bytes(batch, hq, context_size);
+    if (need == 0) return minf::fail(MINF_E_ARG, "bad sizes");
+    if (need > minf::kStaticScratchBytes)
+        return minf::fail(MINF_E_UNSUPPORTED,
+                          "problem needs %zu bytes of scratch, the built-in scratch holds %zu "
+                          "(batch*heads*tokens of about one million); use minf_vs_estimate with a caller buffer",
+                          need, minf::kStaticScratchBytes);
+    void* scratch = nullptr;
+    int rc = minf::static_scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    return minf_vs_estimate(q, k, q_strides, k_strides, batch, hq, hkv, context_size, head_dim,
+                            vertical_size, slash_size, cap_v, cap_s, v_idx_out, s_idx_out, nnz_v_out, nnz_s_out,
+                            nullptr, nullptr, scratch, status, stream);
+}
