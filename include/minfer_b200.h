@@ -76,6 +76,19 @@ int minf_vs_build_plan(
     void* plan, int32_t* status, void* stream);
 
 /*
+ * The same for a window of the sequence: the plan covers the n_q query rows that start at
+ * position q_pos0 (a multiple of 64; 256 when the plan feeds minf_sparse_attention_fwd_window).
+ * Used by sequence-sharded callers, which build one plan per local query chunk from the
+ * global index lists.  seqlens still holds the length of the whole sequence.
+ */
+size_t minf_plan_bytes_window(int batch, int heads, int q_pos0, int n_q, int cap_v, int cap_s);
+int minf_vs_build_plan_window(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    const int32_t* nnz_v_per_head, const int32_t* nnz_s_per_head,
+    int batch, int heads, int q_pos0, int n_q, int cap_v, int cap_s,
+    void* plan, int32_t* status, void* stream);
+
+/*
  * Block-sparse plan: top-k key blocks per query block from mean-pooled Q and K.  Replaces
  * _build_block_index (ops/block_sparse_flash_attention.py:151-166) including the padding
  * rule of its caller (:178).  Only heads whose head_mode entry is MINF_MODE_PLAN and whose
@@ -121,6 +134,31 @@ int minf_vs_estimate(
     void* scratch, int32_t* status, void* stream);
 
 /*
+ * The three stages of minf_vs_estimate as separate calls, for callers that hold only part of
+ * the keys (sequence sharding): statistics pass over the local keys, exchange of the per-chunk
+ * statistics, score pass, reduction of the score arrays over the ranks, selection.
+ *   q_last   the last min(64, context_size) queries of every head, [batch, hq, last_q, 128]
+ *   k        the n_k local keys at positions [col_base, col_base + n_k) (col_base % 128 == 0)
+ *   stats    float2 [batch*hq][64][chunks_total]; this call owns chunks
+ *            [chunk_offset, chunk_offset + minf_vs_scores_chunks(batch, hq, hkv, n_k)).
+ *            Pass 1 writes (row max, row sum) per chunk; pass 2 reads all chunks_total entries.
+ *   vertical_scores / slash_scores   fp32 [batch, hq, context_size], zeroed by the caller before
+ *            pass 2 (slash is indexed by diagonal offset and accumulated with atomics).
+ * No counterpart in the reference beyond minference_forward.py:599-614.
+ */
+int minf_vs_scores_chunks(int batch, int hq, int hkv, int n_k);
+int minf_vs_scores_pass(
+    int pass, const void* q_last, const void* k,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim,
+    void* stats, int chunk_offset, int chunks_total, float* vertical_scores, float* slash_scores,
+    int32_t* status, void* stream);
+int minf_vs_select(
+    const float* vertical_scores, const float* slash_scores, int batch, int hq, int context_size,
+    const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* stream);
+
+/*
  * minf_vs_estimate for callers that cannot provide scratch memory and must not trigger an
  * allocation (a plugin inside a process whose device memory is a pre-carved arena it has no
  * handle to, or a caller on a path where allocators are off limits).  No counterpart in the
@@ -159,6 +197,28 @@ int minf_sparse_attention_fwd(
     const int64_t q_strides[3], const int64_t k_strides[3],
     const int64_t v_strides[3], const int64_t o_strides[3],
     int batch, int hq, int hkv, int context_size, int head_dim, float sm_scale,
+    const int32_t* head_mode, const int32_t* head_param,
+    const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
+    int32_t* status, void* stream);
+
+/*
+ * One (query chunk, key chunk) pair of a sequence-sharded attention.  q/o hold the n_q query
+ * rows at positions [q_pos0, q_pos0 + n_q) (q_pos0 a multiple of 256), k/v hold the n_kv keys
+ * at positions [kv_pos0, kv_pos0 + n_kv) (kv_pos0 a multiple of 64); `plan` was built with
+ * minf_vs_build_plan_window for the same query window; context_size is the length of the whole
+ * sequence.  Keys outside the key window are left to other calls.  `lse` (optional, fp32
+ * [batch, hq, n_q]) receives per row the base-2 logarithm of the sum of 2^(logit * sm_scale *
+ * log2(e)) over the keys this call saw (-inf when it saw none); the output rows are normalised
+ * with that sum, so partial results of several key chunks combine as
+ *   o = sum_i 2^(lse_i - lse) * o_i,   lse = log2(sum_i 2^lse_i).
+ * No counterpart in the reference (it has no sequence parallelism).
+ */
+int minf_sparse_attention_fwd_window(
+    const void* q, const void* k, const void* v, void* o, float* lse,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    const int64_t v_strides[3], const int64_t o_strides[3],
+    int batch, int hq, int hkv, int context_size, int n_q, int q_pos0, int n_kv, int kv_pos0,
+    int head_dim, float sm_scale,
     const int32_t* head_mode, const int32_t* head_param,
     const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
     int32_t* status, void* stream);

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     int32_t* bi = a.block_index ? a.block_index + (bh * a.rows_pad + m) * a.top_k : nullptr;
     int2* rng = nullptr;
     if (a.plan && m < a.rows)
-        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_index(m, a.layout.cap_s);
+        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_offset(a.layout, m);
     if (threadIdx.x == 0) { sh_base = 0; sh_ties = 0; }
     __syncthreads();
     int nrng = 0;          // maintained by thread 0 only

@@ -1,22 +1,35 @@
 // Sparse flash-attention forward for sm_100a: tcgen05 MMA with TMEM accumulators, TMA tile
 // loads for contiguous key ranges, cp.async gathers for vertical columns.
 //
-// One CTA owns 128*NSLOT consecutive query rows of one head (2*NSLOT row blocks of 64, the
-// granularity at which the reference defines its index set,
-// ops/pit_sparse_flash_attention_v2.py:64-153).  Warp roles:
-//   warp 0            producer: walks the plan of its row blocks, merges them into a single
-//                     stream of 64-key steps (a contiguous tile or 64 gathered columns) with
-//                     one 64-bit column mask per row block, and fills the K/V stage ring
-//   warp 1            issues every tcgen05.mma (lane 0) and owns the TMEM allocation
-//   warps 2..5 (+4)   one thread per query row: masks, online softmax in registers, P as
-//                     bf16 into shared memory, final normalisation and store
-// Per step and slot:  S = Q K^T (128x64x128) -> softmax -> O += P V (128x128x64); S is double
-// buffered in TMEM so the next QK^T overlaps the softmax.  The running maximum is only
-// raised when it grows by more than 2^8, which keeps the O rescale in TMEM rare.
+// One CTA owns 256 consecutive query rows of one head (4 row blocks of 64, the granularity at
+// which the reference defines its index set, ops/pit_sparse_flash_attention_v2.py:64-153) as two
+// 128-row slots.  Warp roles (three warpgroups of four warps):
+//   warp 0          producer: merges the plans of the four row blocks into one stream of steps.
+//                   A step is 64 or 128 keys -- a contiguous token range (TMA) or gathered
+//                   vertical columns (cp.async) -- with a 128-bit key mask per row block.
+//                   K and V travel through separate rings so a K stage is recycled as soon as
+//                   both QK^T products have read it.
+//   warp 1          issues every tcgen05.mma (lane 0) and owns the TMEM allocation
+//   warps 2-3       spare (they keep the roles aligned to warpgroups of four; setmaxnreg hands
+//                   their registers to the softmax warps)
+//   warps 4-7/8-11  softmax of slot 0 / slot 1, one thread per query row, the whole 128-key row
+//                   of S in registers
+// TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written back
+// over the first half of S and feeds the PV product straight from TMEM, so it never touches
+// shared memory.  The two slots alternate: while one slot's softmax runs, the tensor pipe
+// executes the other slot's PV and next QK^T.
 //
-// Semantics kept from the reference kernels: causal mask inside contiguous tiles, none in
-// the gathered-column loop, keys >= context masked, fp32 accumulation, P rounded to bf16,
-// 1/sqrt(d) scale applied with exp2.  A row with no visible key yields zeros.
+// Positions are global token positions throughout; `q_pos0` / `kv_pos0` say where the local Q
+// and K/V tensors sit in the sequence, so the same kernel serves a whole sequence on one GPU
+// (both zero) and one (query chunk, key chunk) pair of a sequence-sharded ring step, where keys
+// outside the local chunk are left to another step and the partial results are merged through
+// the per-row log-sum-exp written to `lse`.
+//
+// Semantics kept from the reference kernels: causal mask inside contiguous tiles, none in the
+// gathered-column loop, keys >= context masked, fp32 accumulation, P rounded to bf16,
+// 1/sqrt(d) scale applied with exp2.  A row with no visible key yields zeros (lse = -inf).
+// The running maximum is only raised when it grows by more than 2^8, so the O rescale in TMEM
+// is rare.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -29,112 +42,202 @@
 namespace minf {
 
 constexpr int kHeadDim = 128;
-constexpr uint32_t kQBytes = 128 * 256;     // one 128-row Q tile
-constexpr uint32_t kStageBytes = 2 * 64 * 256;  // K tile + V tile, 64 keys each
-constexpr uint32_t kPBytes = 128 * 128;     // 128 rows x 64 bf16
+constexpr int kNK = 2, kNV = 3, kNM = 8;           // K stages, V stages, step-descriptor ring
+constexpr uint32_t kTile = 128 * 256;              // 128 rows x 128 bf16
+constexpr uint32_t kQOff = 0;
+constexpr uint32_t kKOff = 2 * kTile;
+constexpr uint32_t kVOff = kKOff + kNK * kTile;
+constexpr uint32_t kCtlOff = kVOff + kNV * kTile;
 
-enum StepKind : int { kStepTile = 0, kStepGather = 1, kStepEnd = 2 };
+enum StepKind : int { kTileStep = 0, kGatherStep = 1, kEndStep = 2 };
 
-struct StepMeta {
+struct Step {
     int kind;
-    int t;        // first key of a contiguous tile
-    int pad0, pad1;
-    unsigned long long mask[4];  // per row block of the CTA: which of the 64 keys it may see
+    int t;        // first key (global position) of a contiguous tile
+    int width;    // 64 or 128 keys
+    int pad;
+    unsigned long long mask[4][2];   // per row block: visible keys (bit i of word w = key 64*w + i)
 };
 
-template <int NSLOT>
-struct SmemLayout {
-    static constexpr int kStages = NSLOT == 1 ? 2 : 4;
-    static constexpr uint32_t q_off = 0;
-    static constexpr uint32_t kv_off = NSLOT * kQBytes;
-    static constexpr uint32_t p_off = kv_off + kStages * kStageBytes;
-    static constexpr uint32_t ctl_off = p_off + NSLOT * kPBytes;
-};
-
-template <int NSLOT>
 struct Control {
     unsigned long long q_full;
-    unsigned long long kv_full[SmemLayout<NSLOT>::kStages];
-    unsigned long long kv_empty[SmemLayout<NSLOT>::kStages];
-    unsigned long long s_full[NSLOT][2];
-    unsigned long long p_full[NSLOT];
-    unsigned long long pv_done[NSLOT];
+    unsigned long long k_full[kNK], k_empty[kNK], v_full[kNV], v_empty[kNV];
+    unsigned long long m_full[kNM], m_empty[kNM];
+    unsigned long long s_full[2], p_full[2], o_done[2];
     uint32_t tmem_base;
     int abort;
-    StepMeta step[SmemLayout<NSLOT>::kStages];
-    int colring[128];
+    Step step[kNM];
+    int colring[256];
 };
 
 struct AttnArgs {
     __nv_bfloat16* o;
     const __nv_bfloat16* k;
     const __nv_bfloat16* v;
+    float* lse;                       // optional [batch, hq, n_q], base-2 log-sum-exp of the scaled logits
     long long o_sb, o_sh, o_sn;
     long long k_sb, k_sh, k_sn;
     long long v_sb, v_sh, v_sn;
-    int batch, hq, hkv, n_ctx, rows;
+    int batch, hq, hkv;
+    int n_ctx;                        // length of the whole sequence
+    int n_q, q_pos0;                  // local query rows and the position of the first one
+    int n_kv, kv_pos0;                // local keys and the position of the first one
     float scale_log2;                 // sm_scale * log2(e)
     const int32_t* head_mode;
     const int32_t* head_param;
-    const unsigned char* plan;
+    const unsigned char* plan;        // covers the row blocks of the local queries
     PlanLayout layout;
     const int32_t* v_idx;
     int cap_v;
-    int items_per_head;               // CTAs per (batch, head)
+    int items_per_head;
     int32_t* status;
 };
 
-// Cursor over the merged ranges of one row block, 32 ranges buffered across the warp.
-struct RangeCursor {
-    const int2* rng;
-    int n;         // number of ranges
-    int ri;        // current range
-    int base;      // first range held in `buf`
-    int2 buf;      // lane l holds range base + l
-    int a, b;      // current range, a already advanced past consumed keys
-    int last_row;  // last query row of the row block
-
-    __device__ __forceinline__ void fetch(int lane) {
-        if (ri >= n) { a = INT32_MAX; b = INT32_MAX; return; }
-        if (ri - base >= 32 || ri < base) {
-            base = ri;
-            buf = (base + lane < n) ? rng[base + lane] : make_int2(INT32_MAX, INT32_MAX);
-        }
-        a = __shfl_sync(0xffffffffu, buf.x, ri - base);
-        b = __shfl_sync(0xffffffffu, buf.y, ri - base);
-    }
-    __device__ __forceinline__ void init(const int2* r, int count, int last, int lane) {
-        rng = r; n = count; ri = 0; base = -64; last_row = last;
-        fetch(lane);
-    }
-    __device__ __forceinline__ bool live(int n_ctx) const { return ri < n && a <= last_row && a < n_ctx; }
+struct Maps {
+    CUtensorMap q, k64, k128, v64, v128;
 };
 
-__device__ __forceinline__ unsigned long long bit_span(int lo, int hi) {  // bits [lo, hi), 0 <= lo < hi <= 64
-    const unsigned long long upper = hi >= 64 ? ~0ull : ((1ull << hi) - 1ull);
-    return upper & (~0ull << lo);
+// Cursor over the merged ranges of one row block, clipped to the local key window; 32 ranges
+// are buffered across the warp.
+struct RangeCursor {
+    const int2* rng;
+    int n, ri, base;
+    int2 buf;
+    int a, b;
+    int last_row, kv_lo, kv_hi;
+    __device__ __forceinline__ void fetch(int lane) {
+        for (;;) {
+            if (ri >= n) { a = INT32_MAX; b = INT32_MAX; return; }
+            if (ri - base >= 32 || ri < base) {
+                base = ri;
+                buf = (base + lane < n) ? rng[base + lane] : make_int2(INT32_MAX, INT32_MAX);
+            }
+            a = max(__shfl_sync(0xffffffffu, buf.x, ri - base), kv_lo);
+            b = min(__shfl_sync(0xffffffffu, buf.y, ri - base), kv_hi);
+            if (a < b || a >= kv_hi) return;     // usable, or everything from here on lies past the window
+            ++ri;                                // range entirely before the window
+        }
+    }
+    __device__ __forceinline__ void init(const int2* r, int count, int last, int lo, int hi, int lane) {
+        rng = r; n = count; ri = 0; base = -64; last_row = last; kv_lo = lo; kv_hi = hi;
+        fetch(lane);
+    }
+    __device__ __forceinline__ bool live() const { return ri < n && a <= last_row && a < kv_hi; }
+};
+
+__device__ __forceinline__ unsigned long long below64(int x) {   // bits [0, x) for any integer x
+    return x >= 64 ? ~0ull : (x <= 0 ? 0ull : ((1ull << x) - 1ull));
+}
+// bits [lo, hi) of a 128-bit mask are added to (w0, w1)
+__device__ __forceinline__ void span128(int lo, int hi, unsigned long long& w0, unsigned long long& w1) {
+    w0 |= below64(hi) & ~below64(lo);
+    w1 |= below64(hi - 64) & ~below64(lo - 64);
+}
+// keys 0..lim visible (lim may be negative or >= 127)
+__device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigned long long& w1) {
+    w0 = below64(lim + 1);
+    w1 = below64(lim + 1 - 64);
 }
 
-template <int NSLOT>
-__global__ void __launch_bounds__(64 + 128 * NSLOT, NSLOT == 1 ? 2 : 1)
-sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
-    using SL = SmemLayout<NSLOT>;
-    constexpr int NS = SL::kStages;
-    constexpr int NRB = 2 * NSLOT;
+#ifdef MINF_TIMELINE
+// Debug builds only: cycle stamps of one CTA's warps, read back by a probe script.
+__device__ long long* g_timeline = nullptr;
+__device__ int g_timeline_block = 0;
+#define TL(ev, step)                                                                               \
+    do {                                                                                           \
+        if (tl_ptr && tl_n < 2700) {                                                               \
+            tl_ptr[1 + 3 * tl_n] = (ev); tl_ptr[2 + 3 * tl_n] = (step); tl_ptr[3 + 3 * tl_n] = clock64(); \
+            ++tl_n;                                                                                \
+        }                                                                                          \
+    } while (0)
+#define TL_DECL                                                                                    \
+    long long* tl_ptr = (g_timeline && (int)blockIdx.x == g_timeline_block && (threadIdx.x & 31) == 0) \
+                            ? g_timeline + (threadIdx.x >> 5) * 8192 : nullptr;                    \
+    int tl_n = 0;
+#define TL_FLUSH do { if (tl_ptr) tl_ptr[0] = tl_n; } while (0)
+#else
+#define TL(ev, step) do { } while (0)
+#define TL_DECL
+#define TL_FLUSH do { } while (0)
+#endif
+
+// One softmax step of one query row: S (fp32, NCH*32 columns at t_s) -> P (bf16 pairs written
+// back over the first NCH*16 columns).  The whole row is held in registers, so TMEM is read
+// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.
+template <int NCH>
+__device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
+                                            float scale_log2, bool have_o, float& m_ref, float& l_sum) {
+    uint32_t sr[NCH][32];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
+    tmem_wait_ld();
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        if (cm != 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+    }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+    float alpha = 1.f;
+    if (mx > m_ref + 8.f) {          // raise the reference maximum only on a jump of more than 2^8
+        alpha = fast_exp2(m_ref - mx);
+        l_sum *= alpha;
+        m_ref = mx;
+    }
+    const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+    // O of this slot is at rest here: the QK^T that filled S was issued after the previous PV
+    if (have_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            tmem_ld32(t_o + 32 * c, orow);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+            tmem_st32(t_o + 32 * c, orow);
+        }
+    }
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
+            ps4[(i >> 1) & 3] += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(t_s + 16 * c, pk);
+    }
+    l_sum += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+    tmem_wait_st();
+}
+
+__global__ void __launch_bounds__(384, 1)
+sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    Control<NSLOT>* ctl = reinterpret_cast<Control<NSLOT>*>(smem + SL::ctl_off);
+    Control* ctl = reinterpret_cast<Control*>(smem + kCtlOff);
     const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TL_DECL
 
-    // work item: heaviest (latest) rows first; the heads of one item index are neighbours
     const int bh_count = a.batch * a.hq;
-    const int item = a.items_per_head - 1 - (int)(blockIdx.x / bh_count);
+    const int item = a.items_per_head - 1 - (int)(blockIdx.x / bh_count);   // latest rows (most work) first
     const int bh = (int)(blockIdx.x % bh_count);
     const int b = bh / a.hq, h = bh % a.hq;
     const int hk = h / (a.hq / a.hkv);
-    const int rb0 = item * NRB;             // first row block
-    const int row0 = rb0 * 64;              // first query row
+    const int rb_loc0 = item * 4;                   // first row block of the item inside the local queries
+    const int lrow0 = rb_loc0 * 64;                 // first local query row
+    const int row0 = a.q_pos0 + lrow0;              // its position in the sequence
+    const int rows_loc = (a.n_q + 63) / 64;         // row blocks covered by the plan
+    const int kv_lo = a.kv_pos0, kv_hi = a.kv_pos0 + a.n_kv;
 
     // an earlier CTA gave up: leave at once (decision made by one thread so it is uniform)
     if (__syncthreads_or(threadIdx.x == 0 && *(volatile int32_t*)(a.status + MINF_ST_ERROR) != 0)) return;
@@ -142,7 +245,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (threadIdx.x == 0) atomicOr(a.status + MINF_ST_ERROR, 2);
         return;
     }
-
     const int mode = a.head_mode ? a.head_mode[h] : MINF_MODE_PLAN;
     const int n_init = mode == MINF_MODE_ASHAPE ? a.head_param[2 * h] : 0;
     const int n_local = mode == MINF_MODE_ASHAPE ? a.head_param[2 * h + 1] : 0;
@@ -152,21 +254,19 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     if (threadIdx.x == 0) {
         mbar_init(bar(&ctl->q_full), 1);
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(bar(&ctl->kv_full[s]), 1);
-            mbar_init(bar(&ctl->kv_empty[s]), 1 + 4 * NSLOT);
-        }
-        for (int s = 0; s < NSLOT; ++s) {
-            mbar_init(bar(&ctl->s_full[s][0]), 1);
-            mbar_init(bar(&ctl->s_full[s][1]), 1);
+        for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 1); mbar_init(bar(&ctl->k_empty[s]), 1); }
+        for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 1); mbar_init(bar(&ctl->v_empty[s]), 1); }
+        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA lane + 8 softmax warps
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(&ctl->s_full[s]), 1);
             mbar_init(bar(&ctl->p_full[s]), 128);
-            mbar_init(bar(&ctl->pv_done[s]), 1);
+            mbar_init(bar(&ctl->o_done[s]), 1);
         }
         ctl->abort = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(&ctl->tmem_base), 256 * NSLOT);
+        tmem_alloc(smem_u32(&ctl->tmem_base), 512);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -176,412 +276,438 @@ sparse_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         if (lane == 0) {
-            tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-            mbar_arrive_expect_tx(bar(&ctl->q_full), NSLOT * kQBytes);
-            for (int s = 0; s < NSLOT; ++s) {
-                tma_load_4d(smem_base + SL::q_off + s * kQBytes, &tm_q, bar(&ctl->q_full), 0, row0 + 128 * s, h, b);
-                tma_load_4d(smem_base + SL::q_off + s * kQBytes + 16384, &tm_q, bar(&ctl->q_full), 64, row0 + 128 * s, h, b);
+            tma_prefetch_desc(&tm.q); tma_prefetch_desc(&tm.k64); tma_prefetch_desc(&tm.k128);
+            tma_prefetch_desc(&tm.v64); tma_prefetch_desc(&tm.v128);
+            mbar_arrive_expect_tx(bar(&ctl->q_full), 2 * kTile);
+            for (int s = 0; s < 2; ++s) {
+                tma_load_4d(smem_base + kQOff + s * kTile, &tm.q, bar(&ctl->q_full), 0, lrow0 + 128 * s, h, b);
+                tma_load_4d(smem_base + kQOff + s * kTile + 16384, &tm.q, bar(&ctl->q_full), 64, lrow0 + 128 * s, h, b);
             }
         }
         int step = 0;
         bool ok = true;
-        // acquire a stage for `step`; returns stage index or -1 after an abandoned wait
-        auto acquire = [&]() -> int {
-            const int s = step % NS, use = step / NS;
-            if (use > 0 && !mbar_wait(bar(&ctl->kv_empty[s]), (use - 1) & 1, abort_flag)) { ok = false; return -1; }
-            return s;
+        auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
+            const int s = idx % ring, use = idx / ring;
+            if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
+            return true;
         };
-        auto issue_tile = [&](int s, int t) {
+        auto publish = [&](int kind, int t, int width, const unsigned long long (&mk)[4][2]) -> bool {
+            if (!wait_use(ctl->m_empty, kNM, step)) return false;
             if (lane == 0) {
-                const uint32_t dst = smem_base + SL::kv_off + s * kStageBytes;
-                const uint32_t fb = bar(&ctl->kv_full[s]);
-                mbar_arrive_expect_tx(fb, kStageBytes);
-                tma_load_4d(dst, &tm_k, fb, 0, t, hk, b);
-                tma_load_4d(dst + 8192, &tm_k, fb, 64, t, hk, b);
-                tma_load_4d(dst + 16384, &tm_v, fb, 0, t, hk, b);
-                tma_load_4d(dst + 24576, &tm_v, fb, 64, t, hk, b);
+                Step& st = ctl->step[step % kNM];
+                st.kind = kind; st.t = t; st.width = width;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
+                mbar_arrive(bar(&ctl->m_full[step % kNM]));
             }
+            return true;
+        };
+        auto load_tile = [&](int t, int width) -> bool {     // t: global position, inside the local key window
+            const int lt = t - a.kv_pos0;
+            if (!wait_use(ctl->k_empty, kNK, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+            if (!wait_use(ctl->v_empty, kNV, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+            return true;
         };
 
         if (mode == MINF_MODE_ASHAPE) {
-            const int r_hi = min(row0 + 64 * NRB, a.n_ctx) - 1;
+            const int r_hi = min(row0 + 256, a.q_pos0 + a.n_q) - 1;
             int w0 = row0 - n_local + 1;
             w0 = w0 < 0 ? 0 : (w0 & ~63);
             const bool sinks = a.n_ctx > n_local && r_hi >= n_local;
             const int sink_end = sinks ? min(min(n_init, w0), a.n_ctx) : 0;
             for (int phase = 0; phase < 2 && ok; ++phase) {
-                const int t_lo = phase == 0 ? 0 : w0;
-                const int t_hi = phase == 0 ? sink_end : r_hi + 1;
-                for (int t = t_lo; t < t_hi && ok; t += 64) {
-                    const int s = acquire();
-                    if (s < 0) break;
-                    if (lane == 0) {
-                        ctl->step[s].kind = kStepTile;
-                        ctl->step[s].t = t;
+                // sink tiles [0, sink_end), then window tiles [w0, r_hi], both clipped to the local keys
+                const int t_lo = max(phase == 0 ? 0 : w0, kv_lo);
+                const int t_hi = min(phase == 0 ? sink_end : r_hi + 1, kv_hi);
+                for (int t = t_lo; t < t_hi && ok;) {
+                    const int width = (t_hi - t > 64) ? 128 : 64;
+                    // a row block takes part only if one of its rows can see a key of the tile: the
+                    // tile starts at or before its last row and reaches its window (or holds sinks)
+                    unsigned long long mk[4][2];
 #pragma unroll
-                        for (int r = 0; r < 4; ++r) ctl->step[s].mask[r] = ~0ull;
+                    for (int r = 0; r < 4; ++r) {
+                        const int first = row0 + 64 * r, last = first + 63;
+                        const bool sees = last >= t && (phase == 0 || t + width - 1 >= first - n_local + 1 ||
+                                                        (a.n_ctx > n_local && t < n_init));
+                        mk[r][0] = sees ? ~0ull : 0ull;
+                        mk[r][1] = sees ? ~0ull : 0ull;
                     }
-                    __syncwarp();
-                    issue_tile(s, t);
+                    if (!publish(kTileStep, t, width, mk)) break;
+                    if (!load_tile(t, width)) break;
                     ++step;
+                    t += width;
                 }
             }
         } else {
             const unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
             const int32_t* rng_cnt = reinterpret_cast<const int32_t*>(slot);
             const int2* rng_all = reinterpret_cast<const int2*>(slot + a.layout.rng_off);
-            RangeCursor cur[NRB];
+            RangeCursor cur[4];
 #pragma unroll
-            for (int r = 0; r < NRB; ++r) {
-                const int m = rb0 + r;
-                const bool present = m < a.rows;
-                cur[r].init(present ? rng_all + plan_rng_index(m, a.layout.cap_s) : nullptr,
-                            present ? rng_cnt[m] : 0, m * 64 + 63, lane);
+            for (int r = 0; r < 4; ++r) {
+                const int ml = rb_loc0 + r;                       // row block inside the plan
+                const bool present = ml < rows_loc;
+                cur[r].init(present ? rng_all + plan_rng_offset(a.layout, ml) : nullptr,
+                            present ? rng_cnt[ml] : 0, row0 + 64 * r + 63, kv_lo, kv_hi, lane);
             }
-            // ---- contiguous ranges, merged over the row blocks of this CTA
+            // ---- contiguous ranges, merged over the four row blocks
             while (ok) {
                 int t = INT32_MAX;
 #pragma unroll
-                for (int r = 0; r < NRB; ++r)
-                    if (cur[r].live(a.n_ctx)) t = min(t, cur[r].a);
+                for (int r = 0; r < 4; ++r)
+                    if (cur[r].live()) t = min(t, cur[r].a);
                 if (t == INT32_MAX) break;
-                unsigned long long mk[NRB];
+                unsigned long long mk[4][2];
+                unsigned long long any_hi = 0ull;
 #pragma unroll
-                for (int r = 0; r < NRB; ++r) {
-                    mk[r] = 0ull;
-                    // consume every range of this row block that intersects [t, t+64)
-                    while (cur[r].live(a.n_ctx) && cur[r].a < t + 64) {
-                        const int hi = min(cur[r].b, t + 64);
-                        mk[r] |= bit_span(cur[r].a - t, hi - t);
-                        if (cur[r].b <= t + 64) { ++cur[r].ri; cur[r].fetch(lane); }
-                        else { cur[r].a = t + 64; break; }
+                for (int r = 0; r < 4; ++r) {
+                    mk[r][0] = 0ull; mk[r][1] = 0ull;
+                    while (cur[r].live() && cur[r].a < t + 128) {      // every range of the row block inside [t, t+128)
+                        const int hi = min(cur[r].b, t + 128);
+                        span128(cur[r].a - t, hi - t, mk[r][0], mk[r][1]);
+                        if (cur[r].b <= t + 128) { ++cur[r].ri; cur[r].fetch(lane); }
+                        else { cur[r].a = t + 128; break; }
                     }
+                    any_hi |= mk[r][1];
                 }
-                const int s = acquire();
-                if (s < 0) break;
-                if (lane == 0) {
-                    ctl->step[s].kind = kStepTile;
-                    ctl->step[s].t = t;
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) ctl->step[s].mask[r] = r < NRB ? mk[r] : 0ull;
-                }
-                __syncwarp();
-                issue_tile(s, t);
+                const int width = any_hi ? 128 : 64;
+                if (!publish(kTileStep, t, width, mk)) break;
+                TL(1, step);
+                if (!load_tile(t, width)) break;
+                TL(2, step);
                 ++step;
             }
-            // ---- gathered columns: union of the row blocks' bit masks over the vertical list
+            // ---- gathered columns: union of the row blocks' bit masks over the vertical list,
+            //      restricted to columns inside the local key window
             const int words = a.layout.words_v;
             const uint32_t* bits = reinterpret_cast<const uint32_t*>(slot + a.layout.bits_off);
             const int32_t* vlist = a.v_idx ? a.v_idx + (size_t)bh * a.cap_v : nullptr;
-            int filled = 0, emitted = 0;  // entries pushed to the ring / consumed from it
-            auto flush_chunk = [&](int count) {  // gather `count` (<=64) ring entries starting at `emitted`
-                const int s = acquire();
-                if (s < 0) return;
-                const int e0 = ctl->colring[(emitted + lane) & 127];
-                const int e1 = ctl->colring[(emitted + 32 + lane) & 127];
-                const bool v0 = lane < count, v1 = lane + 32 < count;
-                unsigned long long mk[4] = {0ull, 0ull, 0ull, 0ull};
+            int filled = 0, emitted = 0;
+            auto flush_chunk = [&](int count) {   // count <= 128 ring entries starting at `emitted`
+                const int width = count > 64 ? 128 : 64;
+                int e[4];
+                bool val[4];
 #pragma unroll
-                for (int r = 0; r < NRB; ++r) {
-                    const unsigned lo = __ballot_sync(0xffffffffu, v0 && ((e0 >> (28 + r)) & 1));
-                    const unsigned hi = __ballot_sync(0xffffffffu, v1 && ((e1 >> (28 + r)) & 1));
-                    mk[r] = (unsigned long long)lo | ((unsigned long long)hi << 32);
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    val[q4] = lane + 32 * q4 < count;
+                    e[q4] = ctl->colring[(emitted + 32 * q4 + lane) & 255];
                 }
-                if (lane == 0) {
-                    ctl->step[s].kind = kStepGather;
-                    ctl->step[s].t = 0;
+                unsigned long long mk[4][2];
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) ctl->step[s].mask[r] = mk[r];
+                for (int r = 0; r < 4; ++r) {
+                    unsigned bl[4];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) bl[q4] = __ballot_sync(0xffffffffu, val[q4] && ((e[q4] >> (28 + r)) & 1));
+                    mk[r][0] = (unsigned long long)bl[0] | ((unsigned long long)bl[1] << 32);
+                    mk[r][1] = (unsigned long long)bl[2] | ((unsigned long long)bl[3] << 32);
                 }
-                const int c0 = v0 ? (e0 & 0x0fffffff) : 0, c1 = v1 ? (e1 & 0x0fffffff) : 0;
-                const uint32_t kdst = smem_base + SL::kv_off + s * kStageBytes;
-                const __nv_bfloat16* kb = a.k + b * a.k_sb + hk * a.k_sh;
-                const __nv_bfloat16* vb = a.v + b * a.v_sb + hk * a.v_sh;
+                if (!publish(kGatherStep, 0, width, mk)) return;
+                int col[4];      // local key rows
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) col[q4] = val[q4] ? (e[q4] & 0x0fffffff) - a.kv_pos0 : 0;
                 const int chunk = lane & 15, sub = lane >> 4;
+                const int iters = width / 2;
+                if (!wait_use(ctl->k_empty, kNK, step)) return;
+                {
+                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                    const __nv_bfloat16* kb = a.k + b * a.k_sb + hk * a.k_sh;
 #pragma unroll 4
-                for (int it = 0; it < 32; ++it) {
-                    const int r = 2 * it + sub;
-                    const int col = __shfl_sync(0xffffffffu, r < 32 ? c0 : c1, r & 31);
-                    const uint32_t off = (uint32_t)(chunk >> 3) * 8192u + (uint32_t)r * 128u +
-                                         (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
-                    cp_async_16(kdst + off, kb + (long long)col * a.k_sn + chunk * 8);
-                    cp_async_16(kdst + 16384u + off, vb + (long long)col * a.v_sn + chunk * 8);
+                    for (int it = 0; it < iters; ++it) {
+                        const int r = 2 * it + sub;
+                        const int src_lane = r & 31, q4 = r >> 5;
+                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
+                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
+                        cp_async_16(dst + off, kb + (long long)c * a.k_sn + chunk * 8);
+                    }
+                    cp_async_commit();
                 }
-                cp_async_commit();
-                cp_async_wait<0>();
+                if (!wait_use(ctl->v_empty, kNV, step)) { cp_async_wait<0>(); return; }
+                {
+                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                    const __nv_bfloat16* vb = a.v + b * a.v_sb + hk * a.v_sh;
+#pragma unroll 4
+                    for (int it = 0; it < iters; ++it) {
+                        const int r = 2 * it + sub;
+                        const int src_lane = r & 31, q4 = r >> 5;
+                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
+                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
+                        cp_async_16(dst + off, vb + (long long)c * a.v_sn + chunk * 8);
+                    }
+                    cp_async_commit();
+                }
+                cp_async_wait<1>();            // K rows landed
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(&ctl->kv_full[s]));
+                if (lane == 0) mbar_arrive(bar(&ctl->k_full[step % kNK]));
+                cp_async_wait<0>();            // V rows landed
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(&ctl->v_full[step % kNV]));
                 emitted += count;
                 ++step;
             };
             for (int w = 0; w < words && ok; ++w) {
-                uint32_t wr[NRB];
+                uint32_t wr[4];
                 uint32_t any = 0;
 #pragma unroll
-                for (int r = 0; r < NRB; ++r) {
-                    const int m = rb0 + r;
-                    wr[r] = m < a.rows ? bits[(size_t)m * words + w] : 0u;
+                for (int r = 0; r < 4; ++r) {
+                    const int ml = rb_loc0 + r;
+                    wr[r] = ml < rows_loc ? bits[(size_t)ml * words + w] : 0u;
                     any |= wr[r];
                 }
                 if (any == 0u) continue;
-                const bool mine = (any >> lane) & 1u;
-                const int pos = filled + __popc(any & ((1u << lane) - 1u));
-                if (mine) {
-                    int e = vlist[32 * w + lane] & 0x0fffffff;
+                const int vi = 32 * w + lane;
+                const int colv = (((any >> lane) & 1u) && vi < a.cap_v) ? vlist[vi] : -1;
+                const unsigned sel = __ballot_sync(0xffffffffu, colv >= kv_lo && colv < kv_hi);
+                if (sel == 0u) continue;
+                const int pos = filled + __popc(sel & ((1u << lane) - 1u));
+                if ((sel >> lane) & 1u) {
+                    int e = colv & 0x0fffffff;
 #pragma unroll
-                    for (int r = 0; r < NRB; ++r) e |= (int)((wr[r] >> lane) & 1u) << (28 + r);
-                    ctl->colring[pos & 127] = e;
+                    for (int r = 0; r < 4; ++r) e |= (int)((wr[r] >> lane) & 1u) << (28 + r);
+                    ctl->colring[pos & 255] = e;
                 }
-                filled += __popc(any);
+                filled += __popc(sel);
                 __syncwarp();
-                if (filled - emitted >= 64) flush_chunk(64);
+                if (filled - emitted >= 128) flush_chunk(128);
             }
             if (ok && filled > emitted) flush_chunk(filled - emitted);
         }
-        // ---- end marker
         if (ok) {
-            const int s = acquire();
-            if (s >= 0) {
-                if (lane == 0) {
-                    ctl->step[s].kind = kStepEnd;
-                    mbar_arrive(bar(&ctl->kv_full[s]));
-                }
-            }
+            const unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
+            publish(kEndStep, 0, 0, none);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc(128, 64, true, false, false);
-            constexpr uint32_t idesc_o = umma_idesc(128, 128, true, false, true);
-            int ns[NSLOT];       // participating steps issued so far, per slot (S side)
-            int npv[NSLOT];      // per slot (PV side)
-#pragma unroll
-            for (int s = 0; s < NSLOT; ++s) { ns[s] = 0; npv[s] = 0; }
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        {   // every lane follows the control flow, lane 0 issues
+            const bool issuer = lane == 0;
             bool ok = mbar_wait(bar(&ctl->q_full), 0, abort_flag);
-
-            auto part = [&](const StepMeta& m, int slot) { return (m.mask[2 * slot] | m.mask[2 * slot + 1]) != 0ull; };
-            auto issue_s = [&](int stage, int slot) {
-                const uint32_t d = tmem + slot * 256 + 128 + (ns[slot] & 1) * 64;
-                const uint32_t qb = smem_base + SL::q_off + slot * kQBytes;
-                const uint32_t kb = smem_base + SL::kv_off + stage * kStageBytes;
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t ad = umma_desc_sw128(qb + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = umma_desc_sw128(kb + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024);
-                    umma_ss(d, ad, bd, idesc_s, kk > 0);
-                }
-                umma_commit(bar(&ctl->s_full[slot][ns[slot] & 1]));
-                ++ns[slot];
+            // step descriptors are read straight from the shared-memory ring; a slot of the ring is
+            // handed back to the producer only when both query slots are past its step
+            auto kind_of = [&](int j) { return ctl->step[j % kNM].kind; };
+            auto width_of = [&](int j) { return ctl->step[j % kNM].width; };
+            auto part_of = [&](int j, int s) {
+                const Step& st = ctl->step[j % kNM];
+                return (st.mask[2 * s][0] | st.mask[2 * s][1] | st.mask[2 * s + 1][0] | st.mask[2 * s + 1][1]) != 0ull;
             };
-            auto issue_pv = [&](int stage, int slot) {
-                const uint32_t d = tmem + slot * 256;
-                const uint32_t pb = smem_base + SL::p_off + slot * kPBytes;
-                const uint32_t vb = smem_base + SL::kv_off + stage * kStageBytes + 16384;
+            // Descriptor words: the high word (stride offset 1024 B, version 1, 128-byte swizzle) is
+            // constant; the low word is (address >> 4) | (leading offset >> 4) << 16, so walking
+            // along K is an integer add of a compile-time constant.
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+            const uint32_t q_lo[2] = {((smem_base + kQOff) >> 4) | (1u << 16), ((smem_base + kQOff + kTile) >> 4) | (1u << 16)};
+            auto issue_s = [&](int j, int slot, int width) {
+                const uint32_t idesc = width == 128 ? umma_idesc(128, 128, true, false, false)
+                                                    : umma_idesc(128, 64, true, false, false);
+                const uint32_t d = tmem + slot * 256 + 128;
+                const uint32_t a_lo = q_lo[slot];
+                const uint32_t b_lo = ((smem_base + kKOff + (j % kNK) * kTile) >> 4) | (1u << 16);
+                if (issuer) {
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    const uint64_t ad = umma_desc_sw128(pb + kk * 32, 16, 1024);
-                    const uint64_t bd = umma_desc_sw128(vb + kk * 2048, 8192, 1024);
-                    umma_ss(d, ad, bd, idesc_o, (npv[slot] > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
+                        umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
+                    }
+                    umma_commit(bar(&ctl->s_full[slot]));
                 }
-                umma_commit(bar(&ctl->pv_done[slot]));
+            };
+            int npv[2] = {0, 0};
+            auto issue_pv = [&](int j, int slot, int width) {
+                constexpr uint32_t idesc = umma_idesc(128, 128, true, false, true);
+                const uint32_t d = tmem + slot * 256;
+                const uint32_t p = tmem + slot * 256 + 128;
+                const uint32_t b_lo = ((smem_base + kVOff + (j % kNV) * kTile) >> 4) | ((16384u >> 4) << 16);
+                const uint32_t acc0 = npv[slot] > 0 ? 1u : 0u;
+                if (issuer) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, kk > 0 ? 1u : acc0);
+                    if (width == 128) {
+#pragma unroll
+                        for (int kk = 4; kk < 8; ++kk)
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, 1u);
+                    }
+                }
                 ++npv[slot];
             };
 
+            // Steps are issued in order, slot 0 then slot 1: PV(s, j) as soon as P(s, j) is ready,
+            // followed at once by QK^T(s, j+1) so that the slot's next softmax can start while
+            // the other slot's products run.  Waits are blocking (the hardware suspends the
+            // thread), which keeps this warp out of the issue slots of the softmax warps.
+            auto wait_step = [&](int j) { if (ok) ok = mbar_wait(bar(&ctl->m_full[j % kNM]), (j / kNM) & 1, abort_flag); };
             int j = 0;
-            StepMeta cur_m;
-            cur_m.kind = kStepEnd;
-            if (ok) ok = mbar_wait(bar(&ctl->kv_full[0]), 0, abort_flag);
-            if (ok) {
-                cur_m = ctl->step[0];
-                tc_fence_after();
-                if (cur_m.kind != kStepEnd)
-                    for (int s = 0; s < NSLOT; ++s)
-                        if (part(cur_m, s)) issue_s(0, s);
-            }
-            while (ok && cur_m.kind != kStepEnd) {
-                const int stage = j % NS;
-                const int nstage = (j + 1) % NS;
-                StepMeta nxt;
-                ok = mbar_wait(bar(&ctl->kv_full[nstage]), ((j + 1) / NS) & 1, abort_flag);
-                if (!ok) break;
-                nxt = ctl->step[nstage];
-                tc_fence_after();
-                if (nxt.kind != kStepEnd)
-                    for (int s = 0; s < NSLOT; ++s)
-                        if (part(nxt, s)) issue_s(nstage, s);
-                for (int s = 0; s < NSLOT && ok; ++s) {
-                    if (!part(cur_m, s)) continue;
-                    ok = mbar_wait(bar(&ctl->p_full[s]), npv[s] & 1, abort_flag);
-                    if (!ok) break;
+            wait_step(0);
+            if (ok && kind_of(0) != kEndStep) {
+                ok = mbar_wait(bar(&ctl->k_full[0]), 0, abort_flag);
+                if (ok) {
                     tc_fence_after();
-                    issue_pv(stage, s);
+                    for (int s = 0; s < 2; ++s)
+                        if (part_of(0, s)) issue_s(0, s, width_of(0));
+                    if (issuer) umma_commit(bar(&ctl->k_empty[0]));
+                }
+            }
+            while (ok && kind_of(j) != kEndStep) {
+                wait_step(j + 1);
+                if (!ok) break;
+                const bool nxt_live = kind_of(j + 1) != kEndStep;
+                ok = mbar_wait(bar(&ctl->v_full[j % kNV]), (j / kNV) & 1, abort_flag);
+                bool k_ready = false;
+                for (int s = 0; s < 2 && ok; ++s) {
+                    if (part_of(j, s)) {
+                        ok = mbar_wait(bar(&ctl->p_full[s]), npv[s] & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        TL(10 + s, j);
+                        issue_pv(j, s, width_of(j));
+                        TL(12 + s, j);
+                    }
+                    if (nxt_live && part_of(j + 1, s)) {
+                        if (!k_ready) { ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag); k_ready = true; }
+                        if (!ok) break;
+                        tc_fence_after();
+                        TL(20 + s, j + 1);
+                        issue_s(j + 1, s, width_of(j + 1));
+                        TL(22 + s, j + 1);
+                    }
                 }
                 if (!ok) break;
-                umma_commit(bar(&ctl->kv_empty[stage]));
-                cur_m = nxt;
+                if (nxt_live && !k_ready) ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag);
+                if (!ok) break;
+                if (issuer) {
+                    umma_commit(bar(&ctl->v_empty[j % kNV]));
+                    if (nxt_live) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
+                    mbar_arrive(bar(&ctl->m_empty[j % kNM]));
+                }
                 ++j;
             }
+            if (ok && issuer) {
+                mbar_arrive(bar(&ctl->m_empty[j % kNM]));   // the end marker itself
+                umma_commit(bar(&ctl->o_done[0]));
+                umma_commit(bar(&ctl->o_done[1]));
+            }
         }
+    } else if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
-        const int slot = (warp - 2) >> 2;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int slot = (warp - 4) >> 2;
         const int sub = warp & 3;                      // TMEM lane quarter this warp may access
-        const int row_local = 32 * sub + lane;         // 0..127 inside the slot
+        const int row_local = 32 * sub + lane;         // row inside the slot
         const int rb_local = 2 * slot + (row_local >> 6);
-        const int row = row0 + 128 * slot + row_local;
+        const int lrow = lrow0 + 128 * slot + row_local;   // local query row
+        const int row = a.q_pos0 + lrow;                   // position in the sequence
+        const bool row_ok = lrow < a.n_q;
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
         const uint32_t t_o = tmem + slot * 256 + lane_base;
-        const uint32_t p_row = smem_base + SL::p_off + slot * kPBytes + row_local * 128;
+        const uint32_t t_s = t_o + 128;
 
         float m_ref = -INFINITY, l_sum = 0.f;
         int n = 0;
         bool ok = true;
         for (int j = 0; ok; ++j) {
-            const int stage = j % NS;
-            ok = mbar_wait(bar(&ctl->kv_full[stage]), (j / NS) & 1, abort_flag);
+            ok = mbar_wait(bar(&ctl->m_full[j % kNM]), (j / kNM) & 1, abort_flag);
             if (!ok) break;
-            const int kind = ctl->step[stage].kind;
-            if (kind == kStepEnd) break;
-            const int t = ctl->step[stage].t;
-            unsigned long long mask = ctl->step[stage].mask[rb_local];
-            const bool slot_in = (ctl->step[stage].mask[2 * slot] | ctl->step[stage].mask[2 * slot + 1]) != 0ull;
+            const Step& st = ctl->step[j % kNM];
+            const int kind = st.kind;
+            const int t = st.t, width = st.width;
+            unsigned long long m0 = st.mask[rb_local][0], m1 = st.mask[rb_local][1];
+            const bool slot_in = (st.mask[2 * slot][0] | st.mask[2 * slot][1] | st.mask[2 * slot + 1][0] | st.mask[2 * slot + 1][1]) != 0ull;
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(&ctl->kv_empty[stage]));  // metadata read
+            if (lane == 0) mbar_arrive(bar(&ctl->m_empty[j % kNM]));
+            if (kind == kEndStep) break;
             if (!slot_in) continue;
 
-            if (kind == kStepTile) {
-                const int lim = row - t;  // keys t..t+lim are causal
-                unsigned long long cm = lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
-                const int nl = a.n_ctx - t;
-                if (nl < 64) cm &= (1ull << nl) - 1ull;
+            if (kind == kTileStep) {
+                unsigned long long c0, c1;
+                upto128(min(row - t, kv_hi - 1 - t), c0, c1);         // causal and inside the local keys
                 if (mode == MINF_MODE_ASHAPE) {
-                    const int j_lo = row - n_local + 1 - t;
-                    const unsigned long long wm = j_lo <= 0 ? ~0ull : (j_lo >= 64 ? 0ull : (~0ull << j_lo));
-                    const int ns_ = n_init - t;
-                    const unsigned long long sm = ns_ >= 64 ? ~0ull : (ns_ <= 0 ? 0ull : ((1ull << ns_) - 1ull));
-                    mask = cm & (wm | sm);
+                    unsigned long long far0, far1, s0, s1;
+                    upto128(row - n_local - t, far0, far1);           // keys at distance >= n_local ...
+                    upto128(n_init - 1 - t, s0, s1);                  // ... are only visible as sinks
+                    m0 = c0 & (~far0 | s0);
+                    m1 = c1 & (~far1 | s1);
                 } else {
-                    mask &= cm;
+                    m0 &= c0; m1 &= c1;
                 }
             }
-            if (row >= a.n_ctx) mask = 0ull;
+            if (!row_ok) { m0 = 0ull; m1 = 0ull; }
 
-            ok = mbar_wait(bar(&ctl->s_full[slot][n & 1]), (n >> 1) & 1, abort_flag);
+            ok = mbar_wait(bar(&ctl->s_full[slot]), n & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            uint32_t sr[64];
-            {
-                uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[0]);
-                uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sr[32]);
-                const uint32_t t_s = tmem + slot * 256 + 128 + (n & 1) * 64 + lane_base;
-                tmem_ld32(t_s, lo);
-                tmem_ld32(t_s + 32, hi);
-                tmem_wait_ld();
-            }
-            float mx = -INFINITY;
-            if (mask == ~0ull) {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-            } else {
-#pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const float x = ((mask >> c) & 1ull) ? __uint_as_float(sr[c]) : -INFINITY;
-                    sr[c] = __float_as_uint(x);
-                    mx = fmaxf(mx, x);
-                }
-            }
-            mx *= a.scale_log2;  // scale > 0, so the maximum commutes with it
-            float alpha = 1.f;
-            if (mx > m_ref + 8.f) {
-                alpha = fast_exp2(m_ref - mx);  // 0 when m_ref is still -inf
-                l_sum *= alpha;
-                m_ref = mx;
-            }
-            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-            float psum = 0.f;
-            uint32_t pk[32];
-#pragma unroll
-            for (int c = 0; c < 64; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
-                psum += p0 + p1;
-                pk[c >> 1] = pack_bf16x2(p0, p1);
-            }
-            l_sum += psum;
-
-            if (n > 0) {
-                ok = mbar_wait(bar(&ctl->pv_done[slot]), (n - 1) & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t orow[32];
-                        tmem_ld32(t_o + 32 * c, orow);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-                        tmem_st32(t_o + 32 * c, orow);
-                    }
-                    tmem_wait_st();
-                }
-            }
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t dst = p_row + (uint32_t)((c ^ (row_local & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * c]),
-                             "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
-                             : "memory");
-            }
-            fence_proxy_async_smem();
+            TL(1, j);
+            if (width == 128) softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
+            else softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
             tc_fence_before();
             mbar_arrive(bar(&ctl->p_full[slot]));
+            TL(2, j);
             ++n;
         }
 
-        // TMEM loads are warp-collective: run them for the whole warp, store only live rows.
-        {
-            bool warp_ok = __all_sync(0xffffffffu, ok);
-            if (warp_ok && n > 0) {
-                bool w = mbar_wait(bar(&ctl->pv_done[slot]), (n - 1) & 1, abort_flag);
-                warp_ok = __all_sync(0xffffffffu, w);
-            }
-            if (warp_ok) {
-                tc_fence_after();
-                const float inv = (n > 0 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
-                __nv_bfloat16* dst = a.o + b * a.o_sb + h * a.o_sh + (long long)row * a.o_sn;
+        // epilogue: TMEM loads are warp-collective, so the whole warp runs them
+        bool warp_ok = __all_sync(0xffffffffu, ok);
+        if (warp_ok) {
+            const bool w = mbar_wait(bar(&ctl->o_done[slot]), 0, abort_flag);
+            warp_ok = __all_sync(0xffffffffu, w);
+        }
+        if (warp_ok) {
+            tc_fence_after();
+            const bool any_key = n > 0 && l_sum > 0.f;
+            const float inv = any_key ? 1.f / l_sum : 0.f;
+            if (a.lse && row_ok)
+                a.lse[((size_t)b * a.hq + h) * a.n_q + lrow] = any_key ? m_ref + log2f(l_sum) : -INFINITY;
+            __nv_bfloat16* dst = a.o + b * a.o_sb + h * a.o_sh + (long long)lrow * a.o_sn;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t orow[32];
-                    if (n > 0) {
-                        tmem_ld32(t_o + 32 * c, orow);
-                        tmem_wait_ld();
-                    } else {
+            for (int c = 0; c < 4; ++c) {
+                uint32_t orow[32];
+                if (n > 0) {
+                    tmem_ld32(t_o + 32 * c, orow);
+                    tmem_wait_ld();
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = 0u;
-                    }
-                    if (row < a.n_ctx) {
+                    for (int i = 0; i < 32; ++i) orow[i] = 0u;
+                }
+                if (row_ok) {
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 out;
-                            out.x = pack_bf16x2(__uint_as_float(orow[8 * q4 + 0]) * inv, __uint_as_float(orow[8 * q4 + 1]) * inv);
-                            out.y = pack_bf16x2(__uint_as_float(orow[8 * q4 + 2]) * inv, __uint_as_float(orow[8 * q4 + 3]) * inv);
-                            out.z = pack_bf16x2(__uint_as_float(orow[8 * q4 + 4]) * inv, __uint_as_float(orow[8 * q4 + 5]) * inv);
-                            out.w = pack_bf16x2(__uint_as_float(orow[8 * q4 + 6]) * inv, __uint_as_float(orow[8 * q4 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = out;
-                        }
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 out;
+                        out.x = pack_bf16x2(__uint_as_float(orow[8 * q4 + 0]) * inv, __uint_as_float(orow[8 * q4 + 1]) * inv);
+                        out.y = pack_bf16x2(__uint_as_float(orow[8 * q4 + 2]) * inv, __uint_as_float(orow[8 * q4 + 3]) * inv);
+                        out.z = pack_bf16x2(__uint_as_float(orow[8 * q4 + 4]) * inv, __uint_as_float(orow[8 * q4 + 5]) * inv);
+                        out.w = pack_bf16x2(__uint_as_float(orow[8 * q4 + 6]) * inv, __uint_as_float(orow[8 * q4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = out;
                     }
                 }
             }
         }
     }
 
+    TL_FLUSH;
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && ctl->abort) atomicOr(a.status + MINF_ST_ERROR, 1);
-    if (warp == 1) tmem_dealloc(tmem, 256 * NSLOT);
+    if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -623,52 +749,23 @@ int make_tmap_bhnd(CUtensorMap* tm, const void* base, int batch, int heads, int 
     return MINF_OK;
 }
 
-template <int NSLOT>
-static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnArgs a,
-                       cudaStream_t st) {
-    const size_t smem = SmemLayout<NSLOT>::ctl_off + sizeof(Control<NSLOT>);
-    MINF_CUDA_OK(cudaFuncSetAttribute(sparse_attn_fwd_kernel<NSLOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    a.items_per_head = (a.rows + 2 * NSLOT - 1) / (2 * NSLOT);
-    const long long ctas = (long long)a.items_per_head * a.batch * a.hq;
-    if (ctas > 0x7fffffffLL) return fail(MINF_E_UNSUPPORTED, "grid too large");
-    sparse_attn_fwd_kernel<NSLOT><<<(unsigned)ctas, 64 + 128 * NSLOT, smem, st>>>(tq, tk, tv, a);
-    MINF_LAUNCH_OK("sparse_attn_fwd_kernel");
-    return MINF_OK;
+#ifdef MINF_TIMELINE
+extern "C" int minf_debug_timeline(long long* buf, int block) {
+    cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf));
+    cudaMemcpyToSymbol(g_timeline_block, &block, sizeof(block));
+    return 0;
 }
-
-static int attn_slots() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("MINFER_B200_SLOTS");
-        v = (e && e[0] == '2') ? 2 : 1;
-    }
-    return v;
-}
-
-int launch_sparse_attention_v2(const void* q, const void* k, const void* v, void* o,
-                               const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                               const int64_t o_strides[3], int batch, int hq, int hkv, int context_size,
-                               float sm_scale, const int32_t* head_mode, const int32_t* head_param,
-                               const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
-                               int32_t* status, cudaStream_t st);
-
-static int attn_variant() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("MINFER_B200_ATTN");
-        v = (e && e[0] == 'v' && e[1] == '1') ? 1 : 2;
-    }
-    return v;
-}
+#endif
 
 }  // namespace minf
 
 using namespace minf;
 
-extern "C" int minf_sparse_attention_fwd(
-    const void* q, const void* k, const void* v, void* o,
+extern "C" int minf_sparse_attention_fwd_window(
+    const void* q, const void* k, const void* v, void* o, float* lse,
     const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3], const int64_t o_strides[3],
-    int batch, int hq, int hkv, int context_size, int head_dim, float sm_scale,
+    int batch, int hq, int hkv, int context_size, int n_q, int q_pos0, int n_kv, int kv_pos0,
+    int head_dim, float sm_scale,
     const int32_t* head_mode, const int32_t* head_param,
     const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
     int32_t* status, void* stream) {
@@ -678,37 +775,61 @@ extern "C" int minf_sparse_attention_fwd(
     if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1)
         return fail(MINF_E_ARG, "bad sizes: batch=%d hq=%d hkv=%d context=%d", batch, hq, hkv, context_size);
     if (context_size >= (1 << 28)) return fail(MINF_E_UNSUPPORTED, "context_size must be below 2^28");
+    if (n_q < 1 || n_kv < 1 || q_pos0 < 0 || kv_pos0 < 0 || q_pos0 + n_q > context_size || kv_pos0 + n_kv > context_size)
+        return fail(MINF_E_ARG, "query window [%d,+%d) or key window [%d,+%d) outside the context of %d tokens",
+                    q_pos0, n_q, kv_pos0, n_kv, context_size);
+    if ((q_pos0 % 256) || (kv_pos0 % 64))
+        return fail(MINF_E_ARG, "q_pos0 must be a multiple of 256 and kv_pos0 a multiple of 64");
     if (head_mode && !head_param) return fail(MINF_E_ARG, "head_mode given without head_param");
     if (!head_mode && !plan) return fail(MINF_E_ARG, "plan is required when every head uses it");
     if ((reinterpret_cast<uintptr_t>(o) & 15) || (o_strides[0] % 8) || (o_strides[1] % 8) || (o_strides[2] % 8))
         return fail(MINF_E_ARG, "o: base and strides must be 16-byte aligned");
     if (cap_v < 0 || cap_s < 1 || cap_v > (1 << 20)) return fail(MINF_E_ARG, "bad plan capacities");
 
-    if (attn_variant() == 2)
-        return launch_sparse_attention_v2(q, k, v, o, q_strides, k_strides, v_strides, o_strides, batch, hq, hkv,
-                                          context_size, sm_scale, head_mode, head_param, plan, vertical_indexes,
-                                          cap_v, cap_s, status, static_cast<cudaStream_t>(stream));
-    CUtensorMap tq, tk, tv;
+    Maps tm;
     int rc;
-    if ((rc = make_tmap_bhnd(&tq, q, batch, hq, context_size, q_strides, 128, "q"))) return rc;
-    if ((rc = make_tmap_bhnd(&tk, k, batch, hkv, context_size, k_strides, 64, "k"))) return rc;
-    if ((rc = make_tmap_bhnd(&tv, v, batch, hkv, context_size, v_strides, 64, "v"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.q, q, batch, hq, n_q, q_strides, 128, "q"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.k64, k, batch, hkv, n_kv, k_strides, 64, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.k128, k, batch, hkv, n_kv, k_strides, 128, "k"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.v64, v, batch, hkv, n_kv, v_strides, 64, "v"))) return rc;
+    if ((rc = make_tmap_bhnd(&tm.v128, v, batch, hkv, n_kv, v_strides, 128, "v"))) return rc;
 
     AttnArgs a{};
     a.o = static_cast<__nv_bfloat16*>(o);
     a.k = static_cast<const __nv_bfloat16*>(k);
     a.v = static_cast<const __nv_bfloat16*>(v);
+    a.lse = lse;
     a.o_sb = o_strides[0]; a.o_sh = o_strides[1]; a.o_sn = o_strides[2];
     a.k_sb = k_strides[0]; a.k_sh = k_strides[1]; a.k_sn = k_strides[2];
     a.v_sb = v_strides[0]; a.v_sh = v_strides[1]; a.v_sn = v_strides[2];
-    a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size; a.rows = (context_size + 63) / 64;
+    a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size;
+    a.n_q = n_q; a.q_pos0 = q_pos0; a.n_kv = n_kv; a.kv_pos0 = kv_pos0;
     a.scale_log2 = sm_scale * 1.4426950408889634f;
     a.head_mode = head_mode; a.head_param = head_param;
     a.plan = static_cast<const unsigned char*>(plan);
-    a.layout = make_plan_layout(context_size, cap_v, cap_s);
+    a.layout = make_plan_layout_window(q_pos0 / 64, (n_q + 63) / 64, cap_v, cap_s);
     a.v_idx = vertical_indexes; a.cap_v = cap_v;
     a.status = status;
+    a.items_per_head = ((n_q + 63) / 64 + 3) / 4;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (attn_slots() == 2) return launch_attn<2>(tq, tk, tv, a, st);
-    return launch_attn<1>(tq, tk, tv, a, st);
+    const size_t smem = kCtlOff + sizeof(Control);
+    MINF_CUDA_OK(cudaFuncSetAttribute(sparse_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const long long ctas = (long long)a.items_per_head * batch * hq;
+    if (ctas > 0x7fffffffLL) return fail(MINF_E_UNSUPPORTED, "grid too large");
+    sparse_attn_fwd_kernel<<<(unsigned)ctas, 384, smem, st>>>(tm, a);
+    MINF_LAUNCH_OK("sparse_attn_fwd_kernel");
+    return MINF_OK;
+}
+
+extern "C" int minf_sparse_attention_fwd(
+    const void* q, const void* k, const void* v, void* o,
+    const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3], const int64_t o_strides[3],
+    int batch, int hq, int hkv, int context_size, int head_dim, float sm_scale,
+    const int32_t* head_mode, const int32_t* head_param,
+    const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
+    int32_t* status, void* stream) {
+    return minf_sparse_attention_fwd_window(q, k, v, o, nullptr, q_strides, k_strides, v_strides, o_strides,
+                                            batch, hq, hkv, context_size, context_size, 0, context_size, 0,
+                                            head_dim, sm_scale, head_mode, head_param, plan, vertical_indexes,
+                                            cap_v, cap_s, status, stream);
 }

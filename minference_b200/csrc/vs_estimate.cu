@@ -47,9 +47,11 @@ struct EstControl {
 
 struct EstArgs {
     int batch, hq, hkv, n_ctx, last_q;
+    int n_k, col_base;               // local keys and the position of the first one
     int group, pairs_per_group;      // hq / hkv, ceil(group / 2)
-    int tiles, chunks, tiles_per_chunk;
-    float2* stats;                   // [batch*hq][64][chunks]
+    int tiles, chunks, tiles_per_chunk;   // geometry of this call over its local keys
+    int chunk_offset, chunks_total;  // where this call's chunks sit among all chunks of the sequence
+    float2* stats;                   // [batch*hq][64][chunks_total]
     float* vertical;                 // [batch*hq][n_ctx]
     float* slash;                    // [batch*hq][n_ctx], indexed by diagonal offset
     float inv_sqrt_d_div;            // sqrt(d): logits are divided by it
@@ -80,7 +82,7 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int tile_lo = chunk * a.tiles_per_chunk;
     const int tile_hi = min(tile_lo + a.tiles_per_chunk, a.tiles);
     const int ntiles = tile_hi - tile_lo;
-    const int q_start = a.n_ctx - a.last_q;
+    const int q_pos0 = a.n_ctx - a.last_q;          // position of the first of the last_q queries
 
     if (__syncthreads_or(threadIdx.x == 0 && *(volatile int32_t*)(a.status + MINF_ST_ERROR) != 0)) return;
     if ((smem_base & 1023u) != 0u) {
@@ -115,10 +117,10 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // rows 0-63: head h0, rows 64-127: head h0+1 (zero-filled when absent: head coordinate out of range)
             mbar_arrive_expect_tx(bar(&ctl->q_full), kEstQBytes);
             const int h1 = has_h1 ? h0 + 1 : a.hq;   // a.hq is out of range -> zero fill
-            tma_load_4d(smem_base, &tm_q, bar(&ctl->q_full), 0, q_start, h0, b);
-            tma_load_4d(smem_base + 8192, &tm_q, bar(&ctl->q_full), 0, q_start, h1, b);
-            tma_load_4d(smem_base + 16384, &tm_q, bar(&ctl->q_full), 64, q_start, h0, b);
-            tma_load_4d(smem_base + 16384 + 8192, &tm_q, bar(&ctl->q_full), 64, q_start, h1, b);
+            tma_load_4d(smem_base, &tm_q, bar(&ctl->q_full), 0, 0, h0, b);
+            tma_load_4d(smem_base + 8192, &tm_q, bar(&ctl->q_full), 0, 0, h1, b);
+            tma_load_4d(smem_base + 16384, &tm_q, bar(&ctl->q_full), 64, 0, h0, b);
+            tma_load_4d(smem_base + 16384 + 8192, &tm_q, bar(&ctl->q_full), 64, 0, h1, b);
             for (int i = 0; i < ntiles; ++i) {
                 const int s = i & 1, use = i >> 1;
                 if (use > 0 && !mbar_wait(bar(&ctl->k_empty[s]), (use - 1) & 1, abort_flag)) break;
@@ -155,7 +157,7 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int hs = r >> 6, i = r & 63;
         const int h = h0 + hs;
         const bool row_ok = (hs == 0 || has_h1) && i < a.last_q;
-        const int qpos = q_start + i;                // key c is visible iff c <= qpos
+        const int qpos = q_pos0 + i;                 // key c is visible iff c <= qpos
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
         const int tid = threadIdx.x - 64;            // 0..127
         const size_t bh = (size_t)b * a.hq + h;
@@ -164,9 +166,9 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         float row_m = -INFINITY, row_l = 0.f;
         if (PASS == 2 && row_ok) {
             // combine the per-chunk statistics of pass 1 in chunk order
-            const float2* st = a.stats + (bh * 64 + i) * a.chunks;
-            for (int c = 0; c < a.chunks; ++c) row_m = fmaxf(row_m, st[c].x);
-            for (int c = 0; c < a.chunks; ++c)
+            const float2* st = a.stats + (bh * 64 + i) * a.chunks_total;
+            for (int c = 0; c < a.chunks_total; ++c) row_m = fmaxf(row_m, st[c].x);
+            for (int c = 0; c < a.chunks_total; ++c)
                 if (st[c].y > 0.f) row_l += st[c].y * exp2f((st[c].x - row_m) * kLog2e);
         }
         const float inv_l = (PASS == 2 && row_l > 0.f) ? 1.f / row_l : 0.f;
@@ -174,7 +176,8 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bool ok = true;
         for (int it = 0; it < ntiles && ok; ++it) {
             const int s = it & 1, use = it >> 1;
-            const int c0 = (tile_lo + it) * kEstTileN;
+            const int l0 = (tile_lo + it) * kEstTileN;   // first key of the tile inside the local keys
+            const int c0 = a.col_base + l0;              // and its position in the sequence
             ok = mbar_wait(bar(&ctl->s_full[s]), use & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -189,7 +192,7 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int j = 0; j < 32; ++j) {
                     const int c = c0 + q4 * 32 + j;
                     const float v = bf16_round(bf16_round(__uint_as_float(xr[j])) / a.inv_sqrt_d_div);
-                    x[j] = (row_ok && c <= qpos) ? v : -INFINITY;
+                    x[j] = (row_ok && c <= qpos && l0 + q4 * 32 + j < a.n_k) ? v : -INFINITY;
                     mx = fmaxf(mx, x[j]);
                 }
                 if (PASS == 1) {
@@ -216,14 +219,14 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int hh = 0; hh < 2; ++hh) {
                     if (hh == 1 && !has_h1) break;
                     const int c = c0 + tid;
-                    if (c < a.n_ctx) {
+                    if (l0 + tid < a.n_k) {
                         float sum = 0.f;
                         for (int ii = 0; ii < 64; ++ii) sum += ptile[(hh * 64 + ii) * kEstPitch + tid];
                         a.vertical[((size_t)b * a.hq + h0 + hh) * a.n_ctx + c] = sum;
                     }
                     // slash: d = i - j in [-127, 63]; offset = q_start - c0 + d
                     for (int d = tid - 127; d <= 63; d += 128) {
-                        const int off = q_start - c0 + d;
+                        const int off = q_pos0 - c0 + d;
                         if (off < 0 || off >= a.n_ctx) continue;
                         float sum = 0.f;
                         const int i_lo = max(0, d), i_hi = min(63, 127 + d);
@@ -234,7 +237,8 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 named_bar_sync(1, 128);
             }
         }
-        if (PASS == 1 && ok && row_ok && ntiles > 0) a.stats[(bh * 64 + i) * a.chunks + chunk] = make_float2(row_m, row_l);
+        if (PASS == 1 && ok && row_ok && ntiles > 0)
+            a.stats[(bh * 64 + i) * a.chunks_total + a.chunk_offset + chunk] = make_float2(row_m, row_l);
     }
 
     tc_fence_before();
@@ -401,6 +405,74 @@ static void est_geometry(int n_ctx, int* tiles, int* chunks, int* tiles_per_chun
 
 using namespace minf;
 
+extern "C" int minf_vs_scores_chunks(int batch, int hq, int hkv, int n_k) {
+    if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || n_k < 1) return 0;
+    int tiles, chunks, tpc;
+    est_geometry(n_k, &tiles, &chunks, &tpc, hkv * ((hq / hkv + 1) / 2) * batch);
+    return chunks;
+}
+
+extern "C" int minf_vs_scores_pass(
+    int pass, const void* q_last, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim,
+    void* stats, int chunk_offset, int chunks_total, float* vertical_scores, float* slash_scores,
+    int32_t* status, void* stream) {
+    if (!q_last || !k || !stats || !status || (pass == 2 && (!vertical_scores || !slash_scores)))
+        return fail(MINF_E_ARG, "null pointer argument");
+    if (pass != 1 && pass != 2) return fail(MINF_E_ARG, "pass must be 1 or 2");
+    if (head_dim != 128) return fail(MINF_E_UNSUPPORTED, "head_dim must be 128 (got %d)", head_dim);
+    if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1 || batch > 65535 || n_k < 1 ||
+        col_base < 0 || col_base + n_k > context_size)
+        return fail(MINF_E_ARG, "bad sizes");
+    EstArgs a{};
+    a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size;
+    a.last_q = context_size < 64 ? context_size : 64;
+    a.n_k = n_k; a.col_base = col_base;
+    a.group = hq / hkv;
+    a.pairs_per_group = (a.group + 1) / 2;
+    est_geometry(n_k, &a.tiles, &a.chunks, &a.tiles_per_chunk, hkv * a.pairs_per_group * batch);
+    if (chunk_offset < 0 || chunk_offset + a.chunks > chunks_total) return fail(MINF_E_ARG, "chunk window outside the statistics array");
+    a.chunk_offset = chunk_offset; a.chunks_total = chunks_total;
+    a.stats = static_cast<float2*>(stats);
+    a.vertical = vertical_scores; a.slash = slash_scores;
+    a.inv_sqrt_d_div = sqrtf((float)head_dim);
+    a.status = status;
+    CUtensorMap tq, tk;
+    int rc;
+    if ((rc = make_tmap_bhnd(&tq, q_last, batch, hq, a.last_q, q_strides, 64, "q_last"))) return rc;
+    if ((rc = make_tmap_bhnd(&tk, k, batch, hkv, n_k, k_strides, 128, "k"))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = kEstCtlOff + sizeof(EstControl);
+    dim3 grid(a.chunks, hkv * a.pairs_per_group, batch);
+    if (pass == 1) {
+        MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        vs_scores_kernel<1><<<grid, 192, smem, st>>>(tq, tk, a);
+    } else {
+        MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        vs_scores_kernel<2><<<grid, 192, smem, st>>>(tq, tk, a);
+    }
+    MINF_LAUNCH_OK("vs_scores_kernel");
+    return MINF_OK;
+}
+
+extern "C" int minf_vs_select(
+    const float* vertical_scores, const float* slash_scores, int batch, int hq, int context_size,
+    const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* stream) {
+    if (!vertical_scores || !slash_scores || !vertical_size || !slash_size || !v_idx_out || !s_idx_out || !nnz_v_out || !nnz_s_out)
+        return fail(MINF_E_ARG, "null pointer argument");
+    if (batch < 1 || hq < 1 || context_size < 1 || cap_v < 1 || cap_s < 1) return fail(MINF_E_ARG, "bad sizes");
+    SelectArgs s{};
+    s.batch_heads = batch * hq; s.n_ctx = context_size;
+    s.vertical = vertical_scores; s.slash = slash_scores;
+    s.vertical_size = vertical_size; s.slash_size = slash_size;
+    s.cap_v = cap_v; s.cap_s = cap_s;
+    s.v_idx = v_idx_out; s.s_idx = s_idx_out; s.nnz_v = nnz_v_out; s.nnz_s = nnz_s_out;
+    vs_select_kernel<<<dim3(batch * hq, 2), kSelThreads, 0, static_cast<cudaStream_t>(stream)>>>(s);
+    MINF_LAUNCH_OK("vs_select_kernel");
+    return MINF_OK;
+}
+
 extern "C" size_t minf_vs_estimate_scratch_bytes(int batch, int hq, int context_size) {
     if (batch < 1 || hq < 1 || context_size < 1) return 0;
     // chunk count is at most the number of tiles; use that bound so the size does not depend on hkv
@@ -421,52 +493,27 @@ extern "C" int minf_vs_estimate(
     void* scratch, int32_t* status, void* stream) {
     if (!q || !k || !vertical_size || !slash_size || !v_idx_out || !s_idx_out || !nnz_v_out || !nnz_s_out || !scratch || !status)
         return fail(MINF_E_ARG, "null pointer argument");
-    if (head_dim != 128) return fail(MINF_E_UNSUPPORTED, "head_dim must be 128 (got %d)", head_dim);
     if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1 || cap_v < 1 || cap_s < 1 || batch > 65535)
         return fail(MINF_E_ARG, "bad sizes");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-    EstArgs a{};
-    a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size;
-    a.last_q = context_size < 64 ? context_size : 64;
-    a.group = hq / hkv;
-    a.pairs_per_group = (a.group + 1) / 2;
-    const int pair_ctas = hkv * a.pairs_per_group * batch;
-    est_geometry(context_size, &a.tiles, &a.chunks, &a.tiles_per_chunk, pair_ctas);
+    const int chunks = minf_vs_scores_chunks(batch, hq, hkv, context_size);
     unsigned char* sc = static_cast<unsigned char*>(scratch);
-    a.stats = reinterpret_cast<float2*>(sc);
-    size_t off = (size_t)batch * hq * 64 * a.chunks * sizeof(float2);
+    size_t off = (size_t)batch * hq * 64 * chunks * sizeof(float2);
     off = (off + 255) / 256 * 256;
-    a.vertical = vertical_scores_out ? vertical_scores_out : reinterpret_cast<float*>(sc + off);
-    a.slash = slash_scores_out ? slash_scores_out
-                               : reinterpret_cast<float*>(sc + off) + (size_t)batch * hq * context_size;
-    a.inv_sqrt_d_div = sqrtf((float)head_dim);
-    a.status = status;
-
-    CUtensorMap tq, tk;
+    float* vertical = vertical_scores_out ? vertical_scores_out : reinterpret_cast<float*>(sc + off);
+    float* slash = slash_scores_out ? slash_scores_out
+                                    : reinterpret_cast<float*>(sc + off) + (size_t)batch * hq * context_size;
+    // the last min(64, N) queries, viewed in place
+    const int last_q = context_size < 64 ? context_size : 64;
+    const void* q_last = static_cast<const __nv_bfloat16*>(q) + (size_t)(context_size - last_q) * q_strides[2];
+    MINF_CUDA_OK(cudaMemsetAsync(slash, 0, (size_t)batch * hq * context_size * sizeof(float), st));
     int rc;
-    if ((rc = make_tmap_bhnd(&tq, q, batch, hq, context_size, q_strides, 64, "q"))) return rc;
-    if ((rc = make_tmap_bhnd(&tk, k, batch, hkv, context_size, k_strides, 128, "k"))) return rc;
-
-    const size_t smem = kEstCtlOff + sizeof(EstControl);
-    MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MINF_CUDA_OK(cudaMemsetAsync(a.slash, 0, (size_t)batch * hq * context_size * sizeof(float), st));
-    dim3 grid(a.chunks, hkv * a.pairs_per_group, batch);
-    vs_scores_kernel<1><<<grid, 192, smem, st>>>(tq, tk, a);
-    MINF_LAUNCH_OK("vs_scores_kernel<1>");
-    vs_scores_kernel<2><<<grid, 192, smem, st>>>(tq, tk, a);
-    MINF_LAUNCH_OK("vs_scores_kernel<2>");
-
-    SelectArgs s{};
-    s.batch_heads = batch * hq; s.n_ctx = context_size;
-    s.vertical = a.vertical; s.slash = a.slash;
-    s.vertical_size = vertical_size; s.slash_size = slash_size;
-    s.cap_v = cap_v; s.cap_s = cap_s;
-    s.v_idx = v_idx_out; s.s_idx = s_idx_out; s.nnz_v = nnz_v_out; s.nnz_s = nnz_s_out;
-    vs_select_kernel<<<dim3(batch * hq, 2), kSelThreads, 0, st>>>(s);
-    MINF_LAUNCH_OK("vs_select_kernel");
-    return MINF_OK;
+    for (int pass = 1; pass <= 2; ++pass)
+        if ((rc = minf_vs_scores_pass(pass, q_last, k, q_strides, k_strides, batch, hq, hkv, context_size, context_size, 0,
+                                      head_dim, sc, 0, chunks, vertical, slash, status, stream)))
+            return rc;
+    return minf_vs_select(vertical, slash, batch, hq, context_size, vertical_size, slash_size, cap_v, cap_s,
+                          v_idx_out, s_idx_out, nnz_v_out, nnz_s_out, stream);
 }
 
 // ------------------------------------------------------------------------------------------

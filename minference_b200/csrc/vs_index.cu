@@ -36,6 +36,7 @@ struct ConvertArgs {
     const int32_t* nnz_v_per_head;
     const int32_t* nnz_s_per_head;
     int heads, rows, cap_v, cap_s;
+    int rb_base;                      // first row block covered (0 for a whole sequence)
     // REF outputs
     int32_t* block_count;
     int32_t* block_offset;
@@ -64,10 +65,10 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
     for (int i = threadIdx.x; i < nnz_v; i += blockDim.x) v_list[i] = a.v_idx[(size_t)bh * a.cap_v + i];
     __syncthreads();
 
-    const int m = blockIdx.x * kConvertWarps + warp;
+    const int m = blockIdx.x * kConvertWarps + warp;          // row block inside the output
     if (m >= a.rows) return;
     const int seqlen = a.seqlens[b];
-    const int start_m = m * 64, end_m = start_m + 64;
+    const int start_m = (a.rb_base + m) * 64, end_m = start_m + 64;   // its rows in the sequence
     const size_t row = (size_t)bh * a.rows + m;
 
     int32_t* bo = nullptr;
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
         ci = a.column_index + row * a.cap_v;
     } else {
         rng = reinterpret_cast<int2*>(a.plan + (size_t)bh * a.layout.head_bytes + a.layout.rng_off) +
-              plan_rng_index(m, a.layout.cap_s);
+              plan_rng_offset(a.layout, m);
     }
 
     int nblk = 0, ncol = 0, nrng = 0, vp = 0;
@@ -186,7 +187,7 @@ __global__ void plan_count_tiles_kernel(const unsigned char* plan, PlanLayout L,
         const int bh = (int)(gid / L.rows), m = (int)(gid % L.rows);
         const unsigned char* slot = plan + (size_t)bh * L.head_bytes;
         const int n = reinterpret_cast<const int32_t*>(slot)[m];
-        const int2* rng = reinterpret_cast<const int2*>(slot + L.rng_off) + plan_rng_index(m, L.cap_s);
+        const int2* rng = reinterpret_cast<const int2*>(slot + L.rng_off) + plan_rng_offset(L, m);
         for (int i = 0; i < n; ++i) tiles += (rng[i].y - rng[i].x) >> 6;
         const uint32_t* wb = reinterpret_cast<const uint32_t*>(slot + L.bits_off) + (size_t)m * L.words_v;
         int cols = 0;
@@ -242,26 +243,41 @@ extern "C" size_t minf_plan_bytes(int batch, int heads, int context_size, int ca
     return (size_t)make_plan_layout(context_size, cap_v, cap_s).head_bytes * batch * heads;
 }
 
-extern "C" int minf_vs_build_plan(
+extern "C" size_t minf_plan_bytes_window(int batch, int heads, int q_pos0, int n_q, int cap_v, int cap_s) {
+    if (batch < 1 || heads < 1 || q_pos0 < 0 || (q_pos0 % 64) || n_q < 1 || cap_v < 0 || cap_s < 1) return 0;
+    return (size_t)make_plan_layout_window(q_pos0 / 64, (n_q + 63) / 64, cap_v, cap_s).head_bytes * batch * heads;
+}
+
+extern "C" int minf_vs_build_plan_window(
     const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
     const int32_t* nnz_v_per_head, const int32_t* nnz_s_per_head,
-    int batch, int heads, int context_size, int cap_v, int cap_s,
+    int batch, int heads, int q_pos0, int n_q, int cap_v, int cap_s,
     void* plan, int32_t* status, void* stream) {
     if (!seqlens || !vertical_indexes || !slash_indexes || !plan || !status)
         return fail(MINF_E_ARG, "null pointer argument");
-    if (batch < 1 || heads < 1 || context_size < 1 || cap_v < 1 || cap_s < 1 || heads > 65535 || batch > 65535)
-        return fail(MINF_E_ARG, "bad sizes: batch=%d heads=%d context=%d cap_v=%d cap_s=%d", batch, heads,
-                    context_size, cap_v, cap_s);
+    if (batch < 1 || heads < 1 || n_q < 1 || q_pos0 < 0 || (q_pos0 % 64) || cap_v < 1 || cap_s < 1 || heads > 65535 || batch > 65535)
+        return fail(MINF_E_ARG, "bad sizes: batch=%d heads=%d q_pos0=%d n_q=%d cap_v=%d cap_s=%d", batch, heads,
+                    q_pos0, n_q, cap_v, cap_s);
     if (cap_v > 32 * 32 * kMaxBitWordsPerLane)
         return fail(MINF_E_UNSUPPORTED, "cap_v=%d exceeds %d", cap_v, 32 * 32 * kMaxBitWordsPerLane);
     ConvertArgs a{};
     a.seqlens = seqlens; a.v_idx = vertical_indexes; a.s_idx = slash_indexes;
     a.nnz_v_per_head = nnz_v_per_head; a.nnz_s_per_head = nnz_s_per_head;
-    a.heads = heads; a.rows = (context_size + 63) / 64; a.cap_v = cap_v; a.cap_s = cap_s;
+    a.heads = heads; a.rows = (n_q + 63) / 64; a.cap_v = cap_v; a.cap_s = cap_s;
+    a.rb_base = q_pos0 / 64;
     a.plan = static_cast<unsigned char*>(plan);
-    a.layout = make_plan_layout(context_size, cap_v, cap_s);
+    a.layout = make_plan_layout_window(a.rb_base, a.rows, cap_v, cap_s);
     a.status = status;
     return launch_convert(false, a, batch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int minf_vs_build_plan(
+    const int32_t* seqlens, const int32_t* vertical_indexes, const int32_t* slash_indexes,
+    const int32_t* nnz_v_per_head, const int32_t* nnz_s_per_head,
+    int batch, int heads, int context_size, int cap_v, int cap_s,
+    void* plan, int32_t* status, void* stream) {
+    return minf_vs_build_plan_window(seqlens, vertical_indexes, slash_indexes, nnz_v_per_head, nnz_s_per_head,
+                                     batch, heads, 0, context_size, cap_v, cap_s, plan, status, stream);
 }
 
 extern "C" int minf_plan_count_tiles(const void* plan, int batch, int heads, int context_size,
