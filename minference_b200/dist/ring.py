@@ -1,0 +1,241 @@
+"""Zigzag ring attention for sequence-sharded vertical-slash prefill (one process per GPU).
+
+The reference has no sequence parallelism; this module shards one long sequence over the
+ranks of a process group.  The sequence is cut into 2P equal chunks and rank r owns chunks r
+and 2P-1-r of Q, K, V and O, which balances the causal work.  Index estimation needs one
+exchange (the last 64 queries are broadcast, per-chunk softmax statistics are gathered and the
+vertical / slash score arrays are summed over the ranks), after which every rank holds the
+same global index lists and builds the plans of its own query chunks.  The attention itself
+is a ring: in step t a rank holds the K/V shard of rank r-t, attends its two query chunks to
+the shard's two key chunks (pairs that lie entirely in the future are skipped) and passes the
+shard on while it computes.  Partial results of different key chunks are merged through the
+per-row log-sum-exp the kernel writes.
+
+Everything that touches the GPU goes through the C ABI; the orchestration (chunk schedule,
+communication, merge) is plain torch so that it can be exercised on CPU ranks (gloo) with a
+stand-in for the attention call.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _cabi
+
+NEG_INF = float("-inf")
+
+
+# ------------------------------------------------------------------------------ layout
+
+def chunk_size(n_ctx: int, world: int) -> int:
+    c, rem = divmod(n_ctx, 2 * world)
+    if rem or c % 256:
+        raise ValueError(f"the sequence ({n_ctx}) must split into {2 * world} chunks that are multiples of 256 tokens")
+    return c
+
+
+def owned_chunks(rank: int, world: int):
+    return (rank, 2 * world - 1 - rank)
+
+
+def zigzag_split(x: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """``[B,H,N,D]`` (or ``[..., N, D]``) -> the two chunks of ``rank`` concatenated along the token axis."""
+    n = x.shape[-2]
+    c = chunk_size(n, world)
+    a, b = owned_chunks(rank, world)
+    return torch.cat((x[..., a * c:(a + 1) * c, :], x[..., b * c:(b + 1) * c, :]), dim=-2).contiguous()
+
+
+def zigzag_merge(parts, world: int) -> torch.Tensor:
+    """Inverse of ``zigzag_split`` given the local tensors of all ranks in rank order."""
+    c = parts[0].shape[-2] // 2
+    chunks = [None] * (2 * world)
+    for r, p in enumerate(parts):
+        a, b = owned_chunks(r, world)
+        chunks[a], chunks[b] = p[..., :c, :], p[..., c:, :]
+    return torch.cat(chunks, dim=-2)
+
+
+def pair_is_visible(q_chunk: int, kv_chunk: int) -> bool:
+    """A key chunk matters to a query chunk unless it lies entirely in the future."""
+    return kv_chunk <= q_chunk
+
+
+# ------------------------------------------------------------------------------ merge
+
+def merge_partial(acc_o: torch.Tensor, acc_lse: torch.Tensor, o: torch.Tensor, lse: torch.Tensor):
+    """Fold one partial result into the accumulator (base-2 log-sum-exp, see minfer_b200.h).
+
+    ``acc_o`` fp32 ``[B,H,C,D]``, ``acc_lse`` fp32 ``[B,H,C]``; rows that have seen no key carry
+    ``-inf`` and zeros.  Returns the new pair (in place on the accumulators).
+    """
+    new_lse = torch.logaddexp2(acc_lse, lse)
+    safe = torch.where(torch.isinf(new_lse), torch.zeros_like(new_lse), new_lse)
+    w_old = torch.exp2(acc_lse - safe)
+    w_new = torch.exp2(lse - safe)
+    acc_o.mul_(w_old.unsqueeze(-1)).add_(o.float() * w_new.unsqueeze(-1))
+    acc_lse.copy_(new_lse)
+    return acc_o, acc_lse
+
+
+# ------------------------------------------------------------------------------ CUDA pieces
+
+def build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx: int, q_pos0: int, n_q: int):
+    """Plan of the query rows ``[q_pos0, q_pos0 + n_q)`` from the global index lists."""
+    B, H, cap_v = v_idx.shape
+    cap_s = s_idx.shape[2]
+    dev = v_idx.device
+    L = _cabi.lib()
+    plan = torch.empty(L.minf_plan_bytes_window(B, H, q_pos0, n_q, cap_v, cap_s), dtype=torch.uint8, device=dev)
+    status = _cabi.new_status(dev)
+    seqlens = torch.full((B,), n_ctx, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(L.minf_vs_build_plan_window(
+            _cabi.ptr(seqlens), _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
+            B, H, q_pos0, n_q, cap_v, cap_s, _cabi.ptr(plan), _cabi.ptr(status), _cabi.stream_ptr(dev)))
+    return plan, status
+
+
+def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None):
+    """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``."""
+    B, H, n_q, D = q.shape
+    n_kv = k.shape[2]
+    dev = q.device
+    out = torch.empty((B, H, n_q, D), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, H, n_q), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
+            _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse),
+            _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
+            B, H, k.shape[1], n_ctx, n_q, q_pos0, n_kv, kv_pos0, D, float(sm_scale or D ** -0.5),
+            None, None, _cabi.ptr(plan), _cabi.ptr(v_idx), v_idx.shape[2], cap_s,
+            _cabi.ptr(status), _cabi.stream_ptr(dev)))
+    return out, lse
+
+
+def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size: int, slash_size: int, group=None):
+    """Global index lists from sharded K: ``(v_idx, s_idx, nnz_v, nnz_s)``, identical on all ranks."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    B, H, n_loc, D = q_loc.shape
+    Hkv = k_loc.shape[1]
+    dev = q_loc.device
+    c = chunk_size(n_ctx, world)
+    L = _cabi.lib()
+    # the last 64 queries live at the end of rank 0's second chunk
+    q_last = q_loc[:, :, -64:, :].contiguous() if rank == 0 else torch.empty((B, H, 64, D), dtype=q_loc.dtype, device=dev)
+    dist.broadcast(q_last, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    cl = L.minf_vs_scores_chunks(B, H, Hkv, c)
+    stats = torch.zeros((B * H, 64, 2 * cl, 2), dtype=torch.float32, device=dev)
+    stats[..., 0] = NEG_INF
+    status = _cabi.new_status(dev)
+    chunks = owned_chunks(rank, world)
+    k_parts = [k_loc[:, :, :c], k_loc[:, :, c:]]
+
+    def run(pass_, stats_t, offset_of, total, vertical, slash):
+        for i, (ci, kp) in enumerate(zip(chunks, k_parts)):
+            with torch.cuda.device(dev):
+                _cabi.check(L.minf_vs_scores_pass(
+                    pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
+                    B, H, Hkv, n_ctx, c, ci * c, D, _cabi.ptr(stats_t), offset_of(i), total,
+                    _cabi.ptr(vertical), _cabi.ptr(slash), _cabi.ptr(status), _cabi.stream_ptr(dev)))
+
+    run(1, stats, lambda i: i * cl, 2 * cl, None, None)
+    gathered = [torch.empty_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats, group=group)
+    all_stats = torch.cat(gathered, dim=2).contiguous()           # [B*H, 64, world*2*cl, 2]
+    scores = torch.zeros((2, B, H, n_ctx), dtype=torch.float32, device=dev)
+    run(2, all_stats, lambda i: 0, all_stats.shape[2], scores[0], scores[1])
+    dist.all_reduce(scores, group=group)
+    cap_v, cap_s = min(n_ctx, max(vertical_size, 30)), min(n_ctx, max(slash_size, 50))
+    vs = torch.full((B * H,), vertical_size, dtype=torch.int32, device=dev)
+    ss = torch.full((B * H,), slash_size, dtype=torch.int32, device=dev)
+    v_idx = torch.empty((B, H, cap_v), dtype=torch.int32, device=dev)
+    s_idx = torch.empty((B, H, cap_s), dtype=torch.int32, device=dev)
+    nnz_v = torch.empty((B * H,), dtype=torch.int32, device=dev)
+    nnz_s = torch.empty((B * H,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(L.minf_vs_select(_cabi.ptr(scores[0]), _cabi.ptr(scores[1]), B, H, n_ctx, _cabi.ptr(vs), _cabi.ptr(ss),
+                                     cap_v, cap_s, _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
+                                     _cabi.stream_ptr(dev)))
+    _cabi.raise_on_status(status, "ring_vertical_slash_estimate")
+    return v_idx, s_idx, nnz_v, nnz_s
+
+
+# ------------------------------------------------------------------------------ the ring
+
+AttnFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor, int, int, int], tuple]
+
+
+def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None):
+    """Ring schedule, communication and merge.
+
+    ``attn_fn(q_chunk, k_chunk, v_chunk, q_chunk_index, q_pos0, kv_pos0)`` must return the
+    normalised partial output and its base-2 log-sum-exp for the keys it was given.
+    Returns the local output ``[B,H,2C,D]`` in the dtype of ``q_loc``.
+    """
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    c = chunk_size(n_ctx, world)
+    B, H, _, D = q_loc.shape
+    dev = q_loc.device
+    q_chunks = owned_chunks(rank, world)
+    q_parts = [q_loc[:, :, :c], q_loc[:, :, c:]]
+    acc_o = [torch.zeros((B, H, c, D), dtype=torch.float32, device=dev) for _ in range(2)]
+    acc_l = [torch.full((B, H, c), NEG_INF, dtype=torch.float32, device=dev) for _ in range(2)]
+
+    kv = torch.stack((k_loc, v_loc)).contiguous()          # one message per step
+    nxt = torch.empty_like(kv)
+    send_to = (rank + 1) % world
+    recv_from = (rank - 1) % world
+    if group is not None:
+        send_to, recv_from = dist.get_global_rank(group, send_to), dist.get_global_rank(group, recv_from)
+
+    for step in range(world):
+        src = (rank - step) % world
+        reqs = []
+        if step + 1 < world:       # pass the shard on while this step computes
+            ops = [dist.P2POp(dist.isend, kv, send_to, group), dist.P2POp(dist.irecv, nxt, recv_from, group)]
+            reqs = dist.batch_isend_irecv(ops)
+        kv_chunks = owned_chunks(src, world)
+        for qi, qc in enumerate(q_chunks):
+            for ki, kc in enumerate(kv_chunks):
+                if not pair_is_visible(qc, kc):
+                    continue
+                k_part = kv[0][:, :, ki * c:(ki + 1) * c]
+                v_part = kv[1][:, :, ki * c:(ki + 1) * c]
+                o, lse = attn_fn(q_parts[qi], k_part, v_part, qi, qc * c, kc * c)
+                merge_partial(acc_o[qi], acc_l[qi], o, lse)
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            kv, nxt = nxt, kv      # the next receive is ordered after this step's kernels by the stream
+    return torch.cat(acc_o, dim=2).to(q_loc.dtype)
+
+
+def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size: int = 1000, slash_size: int = 6096,
+                                  group=None, indices=None):
+    """Sequence-sharded vertical-slash prefill attention of one layer.
+
+    ``q_loc [1,Hq,2C,128]``, ``k_loc / v_loc [1,Hkv,2C,128]`` hold this rank's two zigzag chunks.
+    ``indices = (v_idx, s_idx, nnz_v, nnz_s)`` skips the distributed estimation (the lists must be
+    the sorted int32 global lists, identical on all ranks).
+    """
+    _cabi.require_cuda(q_loc, k_loc, v_loc)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    c = chunk_size(n_ctx, world)
+    if indices is None:
+        indices = ring_vertical_slash_estimate(q_loc, k_loc, n_ctx, vertical_size, slash_size, group)
+    v_idx, s_idx, nnz_v, nnz_s = indices
+    plans = []
+    for qc in owned_chunks(rank, world):
+        plans.append(build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx, qc * c, c))
+
+    def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
+        plan, status = plans[qi]
+        return attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, s_idx.shape[2], status)
+
+    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
+    for plan, status in plans:
+        _cabi.raise_on_status(status, "ring_vertical_slash_attention")
+    return out

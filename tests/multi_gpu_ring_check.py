@@ -1,0 +1,50 @@
+"""Launched by torchrun with one process per GPU (see tests/test_gpu_ring.py and bench.py):
+runs the sequence-sharded vertical-slash attention, including the distributed index estimation,
+and compares with the whole-sequence kernels on rank 0."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    from minference_b200.dist import ring
+    from minference_b200.modules.minference_forward import vertical_slash_estimate
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import make_qkv
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    n, hq, hkv = 256 * 2 * world * 8, 8, 2
+    q, k, v = make_qkv(n, hq, hkv, seed=3, dtype=torch.bfloat16)          # same tensors on every rank (CPU generator)
+    q_loc, k_loc, v_loc = (ring.zigzag_split(t, rank, world).to(dev) for t in (q, k, v))
+    out_loc = ring.ring_vertical_slash_attention(q_loc, k_loc, v_loc, n, 200, 600)
+    gathered = [torch.empty_like(out_loc) for _ in range(world)]
+    dist.all_gather(gathered, out_loc)
+    ok = True
+    if rank == 0:
+        merged = ring.zigzag_merge(gathered, world).float()
+        dq, dk, dv = q.to(dev), k.to(dev), v.to(dev)
+        v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(dq, dk, 200, 600)
+        full = sparse_attention_forward(dq, dk, dv, build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)).float()
+        d = (merged - full).abs()
+        # the index sets may differ in a few near-ties (different summation order of the statistics)
+        print(f"ring vs whole-sequence: max {d.max().item():.3e} mean {d.mean().item():.3e}")
+        ok = d.mean().item() < 2e-3 and torch.isfinite(merged).all().item()
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, src=0)
+    dist.destroy_process_group()
+    if flag.item() != 1:
+        sys.exit(1)
+    if rank == 0:
+        print("RING_OK")
+
+
+if __name__ == "__main__":
+    main()

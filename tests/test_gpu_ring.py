@@ -1,0 +1,121 @@
+"""Sequence-sharded path on the GPU.
+
+On one GPU the ranks are emulated one after the other in a single process (no kernel waits on
+another): every (query chunk, key chunk) pair goes through the windowed C-ABI entry points and
+the partial results are merged, then compared with the whole-sequence kernel and the oracle.
+With two or more GPUs the real ring (NCCL send/recv between processes) is run as well."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("world,n,kind", [(2, 2048, "local"), (2, 4096, "rand"), (4, 4096, "rand")])
+def test_windowed_kernel_pairs_merge_to_full_attention(dev, world, n, kind):
+    from minference_b200 import _cabi
+    from minference_b200.dist import ring
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import local_vs_indices, make_qkv
+    from oracle import reference_math as R
+    from tests.golden.make_golden import index_case
+
+    hq, hkv = 4, 2
+    q, k, v = make_qkv(n, hq, hkv, seed=8, dtype=torch.bfloat16)
+    if kind == "local":
+        vi, si = local_vs_indices(n, hq, 64, 300, seed=4)
+    else:
+        a, b = index_case(3, n, hq, 120, 260, "uniform")
+        b[..., -1] = 0
+        vi, si = torch.from_numpy(a), torch.from_numpy(b)
+    vs, ss = R.presort_indices(vi, si, 1, hq)
+    dq, dk, dv, dvs, dss = (t.to(dev) for t in (q, k, v, vs.contiguous(), ss.contiguous()))
+    full = sparse_attention_forward(dq, dk, dv, build_vertical_slash_plan(dvs, dss, n))
+    c = ring.chunk_size(n, world)
+    parts = []
+    for r in range(world):
+        outs = []
+        for qc in ring.owned_chunks(r, world):
+            plan, status = ring.build_plan_window(dvs, dss, None, None, n, qc * c, c)
+            acc_o = torch.zeros(1, hq, c, 128, device=dev)
+            acc_l = torch.full((1, hq, c), float("-inf"), device=dev)
+            for kc in range(2 * world):
+                if not ring.pair_is_visible(qc, kc):
+                    continue
+                o, lse = ring.attention_window(dq[:, :, qc * c:(qc + 1) * c], dk[:, :, kc * c:(kc + 1) * c],
+                                               dv[:, :, kc * c:(kc + 1) * c], n, qc * c, kc * c, plan, dvs,
+                                               dss.shape[2], status)
+                ring.merge_partial(acc_o, acc_l, o, lse)
+            assert status.tolist() == [0, 0, 0, 0]
+            outs.append(acc_o)
+        parts.append(torch.cat(outs, dim=2))
+    merged = ring.zigzag_merge(parts, world)
+    assert (merged - full.float()).abs().max().item() < 1.5e-2       # two bf16 roundings apart
+    ref, _ = R.vertical_slash_attention_oracle(q.float(), k.float(), v.float(), vi, si)
+    d = (merged.cpu() - ref[:, :, :n]).abs()
+    assert d.max().item() < 2e-2 and d.mean().item() < 2e-3
+
+
+def test_sharded_estimator_stages_match_whole_sequence(dev):
+    """Score passes over key windows + select == minf_vs_estimate on the whole sequence."""
+    from minference_b200 import _cabi
+    from minference_b200.modules.minference_forward import vertical_slash_estimate
+    from minference_b200.synthetic import make_qkv
+
+    n, hq, hkv, world = 4096, 4, 2, 2
+    q, k, _ = make_qkv(n, hq, hkv, seed=12, dtype=torch.bfloat16)
+    dq, dk = q.to(dev), k.to(dev)
+    v_ref, s_ref, nv_ref, ns_ref, vs_ref, ss_ref = vertical_slash_estimate(dq, dk, 200, 600, return_scores=True)
+    L = _cabi.lib()
+    c = n // (2 * world)
+    cl = L.minf_vs_scores_chunks(1, hq, hkv, c)
+    total = 2 * world * cl
+    stats = torch.zeros((hq, 64, total, 2), dtype=torch.float32, device=dev)
+    scores = torch.zeros((2, 1, hq, n), dtype=torch.float32, device=dev)
+    status = _cabi.new_status(dev)
+    q_last = dq[:, :, -64:].contiguous()
+    for pass_ in (1, 2):
+        for ci in range(2 * world):
+            kp = dk[:, :, ci * c:(ci + 1) * c]
+            _cabi.check(L.minf_vs_scores_pass(pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
+                                              1, hq, hkv, n, c, ci * c, 128, _cabi.ptr(stats), ci * cl, total,
+                                              _cabi.ptr(scores[0]), _cabi.ptr(scores[1]), _cabi.ptr(status), _cabi.stream_ptr(dev)))
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert (scores[0] - vs_ref).abs().max().item() < 1e-4 * max(vs_ref[..., 30:].max().item(), 1e-6) + 1e-6
+    assert (scores[1] - ss_ref).abs().max().item() < 1e-4 * max(ss_ref[..., 100:].max().item(), 1e-6) + 1e-6
+    vsz = torch.full((hq,), 200, dtype=torch.int32, device=dev)
+    ssz = torch.full((hq,), 600, dtype=torch.int32, device=dev)
+    v_idx = torch.empty((1, hq, 200), dtype=torch.int32, device=dev)
+    s_idx = torch.empty((1, hq, 600), dtype=torch.int32, device=dev)
+    nnz_v = torch.empty(hq, dtype=torch.int32, device=dev)
+    nnz_s = torch.empty(hq, dtype=torch.int32, device=dev)
+    _cabi.check(L.minf_vs_select(_cabi.ptr(scores[0]), _cabi.ptr(scores[1]), 1, hq, n, _cabi.ptr(vsz), _cabi.ptr(ssz), 200, 600,
+                                 _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s), _cabi.stream_ptr(dev)))
+    for h in range(hq):
+        assert len(set(v_idx[0, h].tolist()) & set(v_ref[0, h].tolist())) >= 198
+        assert len(set(s_idx[0, h].tolist()) & set(s_ref[0, h].tolist())) >= 594
+
+
+def test_real_ring_on_two_gpus():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29517", os.path.join(ROOT, "tests", "multi_gpu_ring_check.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert "RING_OK" in p.stdout
