@@ -16,8 +16,9 @@ Printed JSON (one line, rank 0):
   roofline     the attention kernel alone (CUDA events around its launch, same stream)
   cpu_baseline the CPU oracle (port of the reference's torch path) on a bounded sample
 
-With N > 1 ranks every rank runs the same workload on its own seeded data (replicas: the
-single-GPU path has no exchange step); the value is the sum of the work over the slowest rank's time.
+With N > 1 ranks (torchrun) the default workload is one 1,048,576-token sequence sharded over the
+ranks with the zigzag ring (strong scaling; K/V shards travel by NCCL send/recv); a single-GPU
+workload name with N > 1 runs replicas instead.
 """
 from __future__ import annotations
 
@@ -39,8 +40,15 @@ FLOP_PER_TILE = 4 * 64 * 64 * 128
 WORKLOADS = {
     # name: (tokens, query heads, kv heads, vertical, slash)
     "llama3_8b_128k_vs": (131072, 32, 8, 1000, 6096),
+    "llama3_8b_256k_vs": (262144, 32, 8, 1000, 6096),
     "llama3_8b_32k_vs": (32768, 32, 8, 1000, 6096),
     "llama3_8b_8k_vs": (8192, 32, 8, 1000, 6096),
+    "llama3_8b_1m_vs": (1048576, 32, 8, 1000, 6096),
+}
+# with more than one GPU the sequence is sharded over the ranks (zigzag ring); tokens in total
+RING_WORKLOADS = {
+    "llama3_8b_1m_vs_ring": (1048576, 32, 8, 1000, 6096),
+    "llama3_8b_256k_vs_ring": (262144, 32, 8, 1000, 6096),
 }
 
 
@@ -289,16 +297,128 @@ def run_gpu_arm(args, wl):
         dist.destroy_process_group()
 
 
+def run_ring_arm(args, wl):
+    """N > 1: one sequence sharded over the ranks, zigzag ring attention (strong scaling)."""
+    import torch.distributed as dist
+
+    from minference_b200 import _cabi
+    from minference_b200.cuda import set_status_checks
+    from minference_b200.dist import ring
+    from minference_b200.synthetic import make_qkv_ranges
+
+    n, hq, hkv, vsize, ssize = RING_WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    _cabi.lib()
+    set_status_checks(False)
+    c = ring.chunk_size(n, world)
+    ranges = [(ch * c, c) for ch in ring.owned_chunks(rank, world)]
+    q, k, v = make_qkv_ranges(n, ranges, hq, hkv, seed=0, dtype=torch.bfloat16, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    stats = {"count_tiles": True}
+    ring.ring_vertical_slash_attention(q, k, v, n, vsize, ssize, stats=stats)       # also counts the tiles once
+    tiles_local = stats["tiles"]
+    for _ in range(max(args.warmup - 1, 0)):
+        ring.ring_vertical_slash_attention(q, k, v, n, vsize, ssize)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    stats = {}
+    t0, t1 = ev(), ev()
+    t0.record()
+    for _ in range(args.steps):
+        ring.ring_vertical_slash_attention(q, k, v, n, vsize, ssize, stats=stats)
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = t0.elapsed_time(t1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in stats["attn_events"]) / args.steps
+    launches = len(stats["attn_events"]) // args.steps
+
+    hq_, hk_, hv_ = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq_).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def step_e2e():
+        dq.copy_(hq_, non_blocking=True); dk.copy_(hk_, non_blocking=True); dv.copy_(hv_, non_blocking=True)
+        out = ring.ring_vertical_slash_attention(dq, dk, dv, n, vsize, ssize)
+        ho.copy_(out, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 2))
+    step_e2e()
+    barrier()
+    s0, s1 = ev(), ev()
+    s0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    s1.record()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1) / e2e_steps
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    sums = torch.tensor([float(tiles_local)], dtype=torch.float64, device=dev)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms = times.tolist()
+    all_tiles = sums.item()
+    ms_per_step = total_ms / args.steps
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = tiles_local * FLOP_PER_TILE / (attn_ms * 1e-3) / 1e12
+        rows = n // 64
+        out = {
+            "metric": "sparse_prefill_attn_tflops", "value": all_tiles * FLOP_PER_TILE / (ms_per_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl, "tokens": n, "tokens_per_gpu": n // world, "q_heads": hq, "kv_heads": hkv, "head_dim": 128,
+                       "vertical": vsize, "slash": ssize, "last_q": 64, "l2": "inputs_exceed_l2",
+                       "parallelism": f"zigzag ring over {world} ranks, K/V shards by NCCL send/recv",
+                       "tiles_per_layer": int(all_tiles), "fraction_of_causal_tiles": all_tiles / (hq * rows * (rows + 1) / 2),
+                       "dense_equivalent_tflops": 4.0 * (n * n / 2) * 128 * hq / (ms_per_step * 1e-3) / 1e12,
+                       "ms_attention_kernels_rank0": attn_ms},
+            "e2e": {"value": all_tiles * FLOP_PER_TILE / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in (q, k, v)),
+                    "d2h_bytes_per_step": world * q.numel() * q.element_size()},
+            "gpu_launches": (launches + 2 * 2 + 1 + 2) * args.steps * world,
+            "roofline": {"bound": "tensor", "kernel": "sparse_attn_fwd_kernel", "achieved": achieved, "peak": peaks["sustained"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["sustained"],
+                         "peak_kind": f"bf16 dense sustained per GPU, of {peaks['source']}; rank 0, summed over its {launches} launches per step",
+                         "frac_of_burst": achieved / peaks["burst"], "traffic": None},
+            "cpu_baseline": None,
+            "clocks": clocks,
+        }
+        print(json.dumps(out))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="llama3_8b_128k_vs", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS))
     args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload is None:
+        args.workload = "llama3_8b_128k_vs" if world == 1 else "llama3_8b_1m_vs_ring"
     if args.impl == "reference":
-        run_reference_arm(args, args.workload)
+        # the CPU arm times the same per-tile work; for a ring workload it uses the single-GPU shape of that length
+        wl = args.workload if args.workload in WORKLOADS else args.workload.replace("_ring", "")
+        run_reference_arm(args, wl)
+    elif args.workload in RING_WORKLOADS:
+        if world < 2:
+            raise SystemExit("ring workloads need torchrun with two or more ranks")
+        run_ring_arm(args, args.workload)
     else:
         run_gpu_arm(args, args.workload)
 

@@ -230,6 +230,9 @@ int minf_sparse_attention_fwd_window(
  */
 int minf_plan_count_tiles(const void* plan, int batch, int heads, int context_size,
                           int cap_v, int cap_s, unsigned long long* tiles_out, void* stream);
+/* The same for a plan built with minf_vs_build_plan_window. */
+int minf_plan_count_tiles_window(const void* plan, int batch, int heads, int q_pos0, int n_q,
+                                 int cap_v, int cap_s, unsigned long long* tiles_out, void* stream);
 
 #ifdef __cplusplus
 }

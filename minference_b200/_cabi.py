@@ -51,6 +51,7 @@ SIGNATURES = {
     "minf_sparse_attention_fwd_window": (c_int, [c_void_p] * 5 + [_I64x3] * 4 + [c_int] * 9 + [c_float] +
                                          [c_void_p] * 4 + [c_int, c_int] + [c_void_p, c_void_p]),
     "minf_plan_count_tiles": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p]),
+    "minf_plan_count_tiles_window": (c_int, [c_void_p] + [c_int] * 6 + [c_void_p, c_void_p]),
 }
 
 

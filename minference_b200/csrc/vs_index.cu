@@ -280,10 +280,19 @@ extern "C" int minf_vs_build_plan(
                                      batch, heads, 0, context_size, cap_v, cap_s, plan, status, stream);
 }
 
+extern "C" int minf_plan_count_tiles_window(const void* plan, int batch, int heads, int q_pos0, int n_q,
+                                            int cap_v, int cap_s, unsigned long long* tiles_out, void* stream);
+
 extern "C" int minf_plan_count_tiles(const void* plan, int batch, int heads, int context_size,
                                      int cap_v, int cap_s, unsigned long long* tiles_out, void* stream) {
+    return minf_plan_count_tiles_window(plan, batch, heads, 0, context_size, cap_v, cap_s, tiles_out, stream);
+}
+
+extern "C" int minf_plan_count_tiles_window(const void* plan, int batch, int heads, int q_pos0, int n_q,
+                                            int cap_v, int cap_s, unsigned long long* tiles_out, void* stream) {
     if (!plan || !tiles_out) return fail(MINF_E_ARG, "null pointer argument");
-    PlanLayout L = make_plan_layout(context_size, cap_v, cap_s);
+    if (q_pos0 < 0 || (q_pos0 % 64) || n_q < 1) return fail(MINF_E_ARG, "bad query window");
+    PlanLayout L = make_plan_layout_window(q_pos0 / 64, (n_q + 63) / 64, cap_v, cap_s);
     const long long total = (long long)L.rows * batch * heads;
     if (total > INT_MAX) return fail(MINF_E_UNSUPPORTED, "too many row blocks");
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -98,6 +98,15 @@ def build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx: int, q_pos0: int, n_q: 
     return plan, status
 
 
+def count_tiles_window(plan, batch: int, heads: int, q_pos0: int, n_q: int, cap_v: int, cap_s: int) -> int:
+    """64x64 tiles of the reference index set for the rows a window plan covers."""
+    out = torch.zeros(1, dtype=torch.int64, device=plan.device)
+    with torch.cuda.device(plan.device):
+        _cabi.check(_cabi.lib().minf_plan_count_tiles_window(_cabi.ptr(plan), batch, heads, q_pos0, n_q, cap_v, cap_s,
+                                                             _cabi.ptr(out), _cabi.stream_ptr(plan.device)))
+    return int(out.item())
+
+
 def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None):
     """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``."""
     B, H, n_q, D = q.shape
@@ -214,7 +223,7 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None)
 
 
 def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size: int = 1000, slash_size: int = 6096,
-                                  group=None, indices=None):
+                                  group=None, indices=None, stats: Optional[dict] = None):
     """Sequence-sharded vertical-slash prefill attention of one layer.
 
     ``q_loc [1,Hq,2C,128]``, ``k_loc / v_loc [1,Hkv,2C,128]`` hold this rank's two zigzag chunks.
@@ -233,9 +242,20 @@ def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size
 
     def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
         plan, status = plans[qi]
-        return attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, s_idx.shape[2], status)
+        if stats is not None:      # CUDA-event timing of the attention launches (benchmarks)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        res = attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, s_idx.shape[2], status)
+        if stats is not None:
+            e1.record()
+            stats.setdefault("attn_events", []).append((e0, e1))
+        return res
 
     out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
+    if stats is not None and stats.get("count_tiles"):
+        B, H = q_loc.shape[0], q_loc.shape[1]
+        stats["tiles"] = sum(count_tiles_window(plan, B, H, qc * c, c, v_idx.shape[2], s_idx.shape[2])
+                             for (plan, _), qc in zip(plans, owned_chunks(rank, world)))
     for plan, status in plans:
         _cabi.raise_on_status(status, "ring_vertical_slash_attention")
     return out
