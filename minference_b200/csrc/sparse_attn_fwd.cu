@@ -118,8 +118,8 @@ struct RangeCursor {
             ++ri;                                // range entirely before the window
         }
     }
-    __device__ __forceinline__ void init(const int2* r, int count, int last, int lo, int hi, int lane) {
-        rng = r; n = count; ri = 0; base = -64; last_row = last; kv_lo = lo; kv_hi = hi;
+    __device__ __forceinline__ void init(const int2* r, int count, int first, int last, int lo, int hi, int lane) {
+        rng = r; n = count; ri = first; base = -64; last_row = last; kv_lo = lo; kv_hi = hi;
         fetch(lane);
     }
     __device__ __forceinline__ bool live() const { return ri < n && a <= last_row && a < kv_hi; }
@@ -361,13 +361,34 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             const int32_t* rng_cnt = reinterpret_cast<const int32_t*>(slot);
             const int2* rng_all = reinterpret_cast<const int2*>(slot + a.layout.rng_off);
             RangeCursor cur[4];
+            const int2* rp[4];
+            int rn[4], first[4], hi_[4];
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int ml = rb_loc0 + r;                       // row block inside the plan
                 const bool present = ml < rows_loc;
-                cur[r].init(present ? rng_all + plan_rng_offset(a.layout, ml) : nullptr,
-                            present ? rng_cnt[ml] : 0, row0 + 64 * r + 63, kv_lo, kv_hi, lane);
+                rp[r] = present ? rng_all + plan_rng_offset(a.layout, ml) : nullptr;
+                rn[r] = present ? rng_cnt[ml] : 0;
+                first[r] = 0; hi_[r] = rn[r];
             }
+            if (kv_lo > 0) {
+                // first range that ends after the start of the key window (ranges are ascending and
+                // disjoint); the four searches advance together so their loads overlap
+                bool more = true;
+                while (more) {
+                    more = false;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (first[r] < hi_[r]) {
+                            const int mid = (first[r] + hi_[r]) >> 1;
+                            if (rp[r][mid].y <= kv_lo) first[r] = mid + 1; else hi_[r] = mid;
+                            more = true;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) cur[r].init(rp[r], rn[r], first[r], row0 + 64 * r + 63, kv_lo, kv_hi, lane);
             // ---- contiguous ranges, merged over the four row blocks
             while (ok) {
                 int t = INT32_MAX;
