@@ -63,7 +63,7 @@ struct Control {
     unsigned long long q_full;
     unsigned long long k_full[kNK], k_empty[kNK], v_full[kNV], v_empty[kNV];
     unsigned long long m_full[kNM], m_empty[kNM];
-    unsigned long long s_full[2], p_full[2], o_done[2];
+    unsigned long long s_full[2], p_half[2][2], o_done[2];   // P is published in two halves per step
     uint32_t tmem_base;
     int abort;
     Step step[kNM];
@@ -166,7 +166,8 @@ __device__ int g_timeline_block = 0;
 // once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.
 template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
-                                            float scale_log2, bool have_o, float& m_ref, float& l_sum) {
+                                            float scale_log2, bool have_o, float& m_ref, float& l_sum,
+                                            uint32_t bar_half0, uint32_t bar_half1) {
     uint32_t sr[NCH][32];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
@@ -203,21 +204,39 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
             tmem_st32(t_o + 32 * c, orow);
         }
     }
-    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+    // P = 2^(S*scale - m): scale and subtract two keys per instruction, exponentials on the MUFU.
+    // The first half of the keys is published on its own barrier so that the PV product can
+    // start on it while the second half is still being exponentiated.
+    const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
+    uint64_t ps2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
-            ps4[(i >> 1) & 3] += p0 + p1;
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2), x0, x1);
+#ifdef MINF_PROBE_NOEXP   // timing probe only (wrong numbers): how much of the step is the MUFU?
+            const float p0 = x0, p1 = x1;
+#else
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+#endif
+            ps2[(i >> 1) & 3] = add_f32x2(ps2[(i >> 1) & 3], pack_f32x2(p0, p1));
             pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + 16 * c, pk);
+        if (c == NCH / 2 - 1) {
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_half0);
+        }
     }
-    l_sum += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+    float a0, a1;
+    unpack_f32x2(add_f32x2(add_f32x2(ps2[0], ps2[1]), add_f32x2(ps2[2], ps2[3])), a0, a1);
+    l_sum += a0 + a1;
     tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(bar_half1);
 }
 
 __global__ void __launch_bounds__(384, 1)
@@ -259,7 +278,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA lane + 8 softmax warps
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(&ctl->s_full[s]), 1);
-            mbar_init(bar(&ctl->p_full[s]), 128);
+            mbar_init(bar(&ctl->p_half[s][0]), 128);
+            mbar_init(bar(&ctl->p_half[s][1]), 128);
             mbar_init(bar(&ctl->o_done[s]), 1);
         }
         ctl->abort = 0;
@@ -552,23 +572,29 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
             };
             int npv[2] = {0, 0};
-            auto issue_pv = [&](int j, int slot, int width) {
+            // PV product of one half of a step's keys (P arrives in two halves, see softmax_row)
+            auto issue_pv_half = [&](int j, int slot, int width, int half) {
                 constexpr uint32_t idesc = umma_idesc(128, 128, true, false, true);
                 const uint32_t d = tmem + slot * 256;
                 const uint32_t p = tmem + slot * 256 + 128;
                 const uint32_t b_lo = ((smem_base + kVOff + (j % kNV) * kTile) >> 4) | ((16384u >> 4) << 16);
-                const uint32_t acc0 = npv[slot] > 0 ? 1u : 0u;
+                const uint32_t acc0 = (npv[slot] > 0 || half > 0) ? 1u : 0u;
                 if (issuer) {
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, kk > 0 ? 1u : acc0);
                     if (width == 128) {
 #pragma unroll
-                        for (int kk = 4; kk < 8; ++kk)
-                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, 1u);
+                        for (int i = 0; i < 4; ++i) {
+                            const int kk = 4 * half + i;
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const int kk = 2 * half + i;
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                        }
                     }
                 }
-                ++npv[slot];
+                if (half == 1) ++npv[slot];
             };
 
             // Steps are issued in order, slot 0 then slot 1: PV(s, j) as soon as P(s, j) is ready,
@@ -588,18 +614,25 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
             }
             while (ok && kind_of(j) != kEndStep) {
+                TL(30, j);
                 wait_step(j + 1);
                 if (!ok) break;
+                TL(31, j);
                 const bool nxt_live = kind_of(j + 1) != kEndStep;
                 ok = mbar_wait(bar(&ctl->v_full[j % kNV]), (j / kNV) & 1, abort_flag);
+                TL(32, j);
                 bool k_ready = false;
                 for (int s = 0; s < 2 && ok; ++s) {
                     if (part_of(j, s)) {
-                        ok = mbar_wait(bar(&ctl->p_full[s]), npv[s] & 1, abort_flag);
+                        ok = mbar_wait(bar(&ctl->p_half[s][0]), npv[s] & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
                         TL(10 + s, j);
-                        issue_pv(j, s, width_of(j));
+                        issue_pv_half(j, s, width_of(j), 0);
+                        ok = mbar_wait(bar(&ctl->p_half[s][1]), npv[s] & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv_half(j, s, width_of(j), 1);
                         TL(12 + s, j);
                     }
                     if (nxt_live && part_of(j + 1, s)) {
@@ -678,10 +711,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (!ok) break;
             tc_fence_after();
             TL(1, j);
-            if (width == 128) softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
-            else softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum);
-            tc_fence_before();
-            mbar_arrive(bar(&ctl->p_full[slot]));
+            if (width == 128)
+                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
+            else
+                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
             TL(2, j);
             ++n;
         }
