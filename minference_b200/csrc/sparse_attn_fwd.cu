@@ -51,11 +51,11 @@ constexpr uint32_t kCtlOff = kVOff + kNV * kTile;
 
 enum StepKind : int { kTileStep = 0, kGatherStep = 1, kEndStep = 2 };
 
-struct Step {
+struct alignas(16) Step {
     int kind;
     int t;        // first key (global position) of a contiguous tile
     int width;    // 64 or 128 keys
-    int pad;
+    int parts;    // bit s set <=> query slot s has a visible key in this step
     unsigned long long mask[4][2];   // per row block: visible keys (bit i of word w = key 64*w + i)
 };
 
@@ -145,8 +145,11 @@ __device__ long long* g_timeline = nullptr;
 __device__ int g_timeline_block = 0;
 #define TL(ev, step)                                                                               \
     do {                                                                                           \
-        if (tl_ptr && tl_n < 2700) {                                                               \
-            tl_ptr[1 + 3 * tl_n] = (ev); tl_ptr[2 + 3 * tl_n] = (step); tl_ptr[3 + 3 * tl_n] = clock64(); \
+        if (tl_ptr) {                                                                              \
+            uint32_t c_;                                                                           \
+            asm volatile("mov.u32 %0, %%clock;" : "=r"(c_));                                       \
+            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(tl_ptr + 1 + tl_n), "r"(c_),     \
+                         "r"((uint32_t)(ev) | ((uint32_t)(step) << 8)));                           \
             ++tl_n;                                                                                \
         }                                                                                          \
     } while (0)
@@ -168,6 +171,12 @@ template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,
                                             uint32_t bar_half0, uint32_t bar_half1) {
+#ifdef MINF_PROBE_NOSOFTMAX   // timing probe only (wrong numbers): the MMA warp's own pace
+    tc_fence_before();
+    mbar_arrive(bar_half0);
+    mbar_arrive(bar_half1);
+    return;
+#endif
     uint32_t sr[NCH][32];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
@@ -317,7 +326,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (!wait_use(ctl->m_empty, kNM, step)) return false;
             if (lane == 0) {
                 Step& st = ctl->step[step % kNM];
-                st.kind = kind; st.t = t; st.width = width;
+                *reinterpret_cast<int4*>(&st) = make_int4(kind, t, width,
+                    ((mk[0][0] | mk[0][1] | mk[1][0] | mk[1][1]) != 0ull ? 1 : 0) |
+                    ((mk[2][0] | mk[2][1] | mk[3][0] | mk[3][1]) != 0ull ? 2 : 0));
 #pragma unroll
                 for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
                 mbar_arrive(bar(&ctl->m_full[step % kNM]));
@@ -335,6 +346,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 tma_load_4d(dst, m, fb, 0, lt, hk, b);
                 tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
             }
+            TL(2, step);
             if (!wait_use(ctl->v_empty, kNV, step)) return false;
             if (lane == 0) {
                 const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
@@ -344,6 +356,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 tma_load_4d(dst, m, fb, 0, lt, hk, b);
                 tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
             }
+            TL(3, step);
             return true;
         };
 
@@ -431,9 +444,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
                 const int width = any_hi ? 128 : 64;
                 if (!publish(kTileStep, t, width, mk)) break;
-                TL(1, step);
                 if (!load_tile(t, width)) break;
-                TL(2, step);
                 ++step;
             }
             // ---- gathered columns: union of the row blocks' bit masks over the vertical list,
@@ -533,65 +544,62 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (ok && filled > emitted) flush_chunk(filled - emitted);
         }
         if (ok) {
+            // the end marker travels like a step: the MMA warp reads a step's descriptor once the
+            // step's K stage is full, so the marker completes a K stage too (with no load)
             const unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
-            publish(kEndStep, 0, 0, none);
+            if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
+                mbar_arrive(bar(&ctl->k_full[step % kNK]));
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-        {   // every lane follows the control flow, lane 0 issues
-            const bool issuer = lane == 0;
-            bool ok = mbar_wait(bar(&ctl->q_full), 0, abort_flag);
-            // step descriptors are read straight from the shared-memory ring; a slot of the ring is
-            // handed back to the producer only when both query slots are past its step
-            auto kind_of = [&](int j) { return ctl->step[j % kNM].kind; };
-            auto width_of = [&](int j) { return ctl->step[j % kNM].width; };
-            auto part_of = [&](int j, int s) {
-                const Step& st = ctl->step[j % kNM];
-                return (st.mask[2 * s][0] | st.mask[2 * s][1] | st.mask[2 * s + 1][0] | st.mask[2 * s + 1][1]) != 0ull;
+        {   // the whole warp follows the control flow and computes the operands; one elected
+            // lane issues each single-thread instruction (see elect_one)
+            auto wait = [&](const unsigned long long* b, int parity) {
+                return __all_sync(0xffffffffu, mbar_wait(bar(b), parity, abort_flag)) != 0;
             };
+            bool ok = wait(&ctl->q_full, 0);
+            // A step's descriptor is written by the producer before it completes the step's K
+            // stage, so waiting for that stage also makes the descriptor visible; it is read once,
+            // as one 16-byte word (kind, first key, width, live slots).
+            auto read_step = [&](int j) { return *reinterpret_cast<const int4*>(&ctl->step[j % kNM]); };
             // Descriptor words: the high word (stride offset 1024 B, version 1, 128-byte swizzle) is
             // constant; the low word is (address >> 4) | (leading offset >> 4) << 16, so walking
             // along K is an integer add of a compile-time constant.
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
             auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
-            const uint32_t q_lo[2] = {((smem_base + kQOff) >> 4) | (1u << 16), ((smem_base + kQOff + kTile) >> 4) | (1u << 16)};
             auto issue_s = [&](int j, int slot, int width) {
                 const uint32_t idesc = width == 128 ? umma_idesc(128, 128, true, false, false)
                                                     : umma_idesc(128, 64, true, false, false);
                 const uint32_t d = tmem + slot * 256 + 128;
-                const uint32_t a_lo = q_lo[slot];
+                const uint32_t a_lo = ((smem_base + kQOff + slot * kTile) >> 4) | (1u << 16);
                 const uint32_t b_lo = ((smem_base + kKOff + (j % kNK) * kTile) >> 4) | (1u << 16);
-                if (issuer) {
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
-                        umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
-                    }
-                    umma_commit(bar(&ctl->s_full[slot]));
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
+                    if (elect_one()) umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
                 }
+                if (elect_one()) umma_commit(bar(&ctl->s_full[slot]));
             };
             int npv[2] = {0, 0};
             // PV product of one half of a step's keys (P arrives in two halves, see softmax_row)
-            auto issue_pv_half = [&](int j, int slot, int width, int half) {
+            auto issue_pv_half = [&](int j, int kv, int slot, int width, int half) {
                 constexpr uint32_t idesc = umma_idesc(128, 128, true, false, true);
                 const uint32_t d = tmem + slot * 256;
                 const uint32_t p = tmem + slot * 256 + 128;
-                const uint32_t b_lo = ((smem_base + kVOff + (j % kNV) * kTile) >> 4) | ((16384u >> 4) << 16);
+                const uint32_t b_lo = ((smem_base + kVOff + kv * kTile) >> 4) | ((16384u >> 4) << 16);
                 const uint32_t acc0 = (npv[slot] > 0 || half > 0) ? 1u : 0u;
-                if (issuer) {
-                    if (width == 128) {
+                if (width == 128) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int kk = 4 * half + i;
-                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
-                        }
-                    } else {
+                    for (int i = 0; i < 4; ++i) {
+                        const int kk = 4 * half + i;
+                        if (elect_one()) umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                    }
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            const int kk = 2 * half + i;
-                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
-                        }
+                    for (int i = 0; i < 2; ++i) {
+                        const int kk = 2 * half + i;
+                        if (elect_one()) umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
                     }
                 }
                 if (half == 1) ++npv[slot];
@@ -601,60 +609,57 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             // followed at once by QK^T(s, j+1) so that the slot's next softmax can start while
             // the other slot's products run.  Waits are blocking (the hardware suspends the
             // thread), which keeps this warp out of the issue slots of the softmax warps.
-            auto wait_step = [&](int j) { if (ok) ok = mbar_wait(bar(&ctl->m_full[j % kNM]), (j / kNM) & 1, abort_flag); };
-            int j = 0;
-            wait_step(0);
-            if (ok && kind_of(0) != kEndStep) {
-                ok = mbar_wait(bar(&ctl->k_full[0]), 0, abort_flag);
-                if (ok) {
-                    tc_fence_after();
+            int j = 0, kv = 0, kv_par = 0;         // kv = j % kNV and the parity of its use
+            int4 cur = make_int4(kEndStep, 0, 0, 0);
+            if (ok) ok = wait(&ctl->k_full[0], 0);
+            if (ok) {
+                cur = read_step(0);
+                if (cur.x != kEndStep) {
+#pragma unroll
                     for (int s = 0; s < 2; ++s)
-                        if (part_of(0, s)) issue_s(0, s, width_of(0));
-                    if (issuer) umma_commit(bar(&ctl->k_empty[0]));
+                        if ((cur.w >> s) & 1) issue_s(0, s, cur.z);
+                    if (elect_one()) umma_commit(bar(&ctl->k_empty[0]));
                 }
             }
-            while (ok && kind_of(j) != kEndStep) {
-                TL(30, j);
-                wait_step(j + 1);
+            while (ok && cur.x != kEndStep) {
+                ok = wait(&ctl->k_full[(j + 1) % kNK], ((j + 1) / kNK) & 1);
                 if (!ok) break;
-                TL(31, j);
-                const bool nxt_live = kind_of(j + 1) != kEndStep;
-                ok = mbar_wait(bar(&ctl->v_full[j % kNV]), (j / kNV) & 1, abort_flag);
+                const int4 nxt = read_step(j + 1);
+                const bool nxt_live = nxt.x != kEndStep;
+                TL(30, j);
+                ok = wait(&ctl->v_full[kv], kv_par);
+                if (!ok) break;
                 TL(32, j);
-                bool k_ready = false;
-                for (int s = 0; s < 2 && ok; ++s) {
-                    if (part_of(j, s)) {
-                        ok = mbar_wait(bar(&ctl->p_half[s][0]), npv[s] & 1, abort_flag);
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    if ((cur.w >> s) & 1) {
+                        ok = wait(&ctl->p_half[s][0], npv[s] & 1);
                         if (!ok) break;
                         tc_fence_after();
                         TL(10 + s, j);
-                        issue_pv_half(j, s, width_of(j), 0);
-                        ok = mbar_wait(bar(&ctl->p_half[s][1]), npv[s] & 1, abort_flag);
+                        issue_pv_half(j, kv, s, cur.z, 0);
+                        ok = wait(&ctl->p_half[s][1], npv[s] & 1);
                         if (!ok) break;
                         tc_fence_after();
-                        issue_pv_half(j, s, width_of(j), 1);
-                        TL(12 + s, j);
+                        TL(14 + s, j);
+                        issue_pv_half(j, kv, s, cur.z, 1);
                     }
-                    if (nxt_live && part_of(j + 1, s)) {
-                        if (!k_ready) { ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag); k_ready = true; }
-                        if (!ok) break;
-                        tc_fence_after();
-                        TL(20 + s, j + 1);
-                        issue_s(j + 1, s, width_of(j + 1));
+                    if (nxt_live && ((nxt.w >> s) & 1)) {
+                        issue_s(j + 1, s, nxt.z);
                         TL(22 + s, j + 1);
                     }
                 }
                 if (!ok) break;
-                if (nxt_live && !k_ready) ok = mbar_wait(bar(&ctl->k_full[(j + 1) % kNK]), ((j + 1) / kNK) & 1, abort_flag);
-                if (!ok) break;
-                if (issuer) {
-                    umma_commit(bar(&ctl->v_empty[j % kNV]));
+                if (elect_one()) {
+                    umma_commit(bar(&ctl->v_empty[kv]));
                     if (nxt_live) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
                     mbar_arrive(bar(&ctl->m_empty[j % kNM]));
                 }
+                cur = nxt;
                 ++j;
+                if (++kv == kNV) { kv = 0; kv_par ^= 1; }
             }
-            if (ok && issuer) {
+            if (ok && elect_one()) {
                 mbar_arrive(bar(&ctl->m_empty[j % kNM]));   // the end marker itself
                 umma_commit(bar(&ctl->o_done[0]));
                 umma_commit(bar(&ctl->o_done[1]));
@@ -686,7 +691,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             const int kind = st.kind;
             const int t = st.t, width = st.width;
             unsigned long long m0 = st.mask[rb_local][0], m1 = st.mask[rb_local][1];
-            const bool slot_in = (st.mask[2 * slot][0] | st.mask[2 * slot][1] | st.mask[2 * slot + 1][0] | st.mask[2 * slot + 1][1]) != 0ull;
+            const bool slot_in = (st.parts >> slot) & 1;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(&ctl->m_empty[j % kNM]));
             if (kind == kEndStep) break;
