@@ -158,7 +158,11 @@ __device__ int g_timeline_block = 0;
                             ? g_timeline + (threadIdx.x >> 5) * 8192 : nullptr;                    \
     int tl_n = 0;
 #define TL_FLUSH do { if (tl_ptr) tl_ptr[0] = tl_n; } while (0)
+#define TL_PARAMS , long long* tl_ptr, int& tl_n, int tl_step
+#define TL_ARGS(j) , tl_ptr, tl_n, (j)
 #else
+#define TL_PARAMS
+#define TL_ARGS(j)
 #define TL(ev, step) do { } while (0)
 #define TL_DECL
 #define TL_FLUSH do { } while (0)
@@ -170,20 +174,21 @@ __device__ int g_timeline_block = 0;
 template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,
-                                            uint32_t bar_half0, uint32_t bar_half1) {
+                                            uint32_t bar_half0, uint32_t bar_half1 TL_PARAMS) {
 #ifdef MINF_PROBE_NOSOFTMAX   // timing probe only (wrong numbers): the MMA warp's own pace
     tc_fence_before();
     mbar_arrive(bar_half0);
     mbar_arrive(bar_half1);
     return;
 #endif
+    // The row maximum of a chunk is taken while the next chunk's load is in flight.
     uint32_t sr[NCH][32];
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
-    tmem_wait_ld();
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    tmem_ld32(t_s, sr[0]);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
+        tmem_wait_ld();
+        if (c + 1 < NCH) tmem_ld32(t_s + 32 * (c + 1), sr[c + 1]);
         const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
         if (cm != 0xffffffffu) {
 #pragma unroll
@@ -191,8 +196,10 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
                 if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+        for (int i = 0; i < 32; i += 2)
+            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
     }
+    TL(40, tl_step);
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
     float alpha = 1.f;
     if (mx > m_ref + 8.f) {          // raise the reference maximum only on a jump of more than 2^8
@@ -201,6 +208,7 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
         m_ref = mx;
     }
     const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+    TL(41, tl_step);
     // O of this slot is at rest here: the QK^T that filled S was issued after the previous PV
     if (have_o && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
@@ -234,6 +242,7 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
             pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + 16 * c, pk);
+        TL(42 + c, tl_step);
         if (c == NCH / 2 - 1) {
             tmem_wait_st();
             tc_fence_before();
@@ -717,9 +726,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             tc_fence_after();
             TL(1, j);
             if (width == 128)
-                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
+                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]) TL_ARGS(j));
             else
-                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
+                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]) TL_ARGS(j));
             TL(2, j);
             ++n;
         }
@@ -732,7 +741,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         }
         if (warp_ok) {
             tc_fence_after();
-            const bool any_key = n > 0 && l_sum > 0.f;
+            const bool any_key = n > 0 && m_ref != -INFINITY;   // the row saw a visible key
             const float inv = any_key ? 1.f / l_sum : 0.f;
             if (a.lse && row_ok)
                 a.lse[((size_t)b * a.hq + h) * a.n_q + lrow] = any_key ? m_ref + log2f(l_sum) : -INFINITY;
