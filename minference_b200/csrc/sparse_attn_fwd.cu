@@ -141,6 +141,7 @@ __device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigne
 
 #ifdef MINF_TIMELINE
 // Debug builds only: cycle stamps of one CTA's warps, read back by a probe script.
+__device__ unsigned long long g_step_stats[8];   // slot-steps: tile128, tile64, gather128, gather64
 __device__ long long* g_timeline = nullptr;
 __device__ int g_timeline_block = 0;
 #define TL(ev, step)                                                                               \
@@ -341,6 +342,15 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
 #pragma unroll
                 for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
                 mbar_arrive(bar(&ctl->m_full[step % kNM]));
+#ifdef MINF_TIMELINE
+                if (kind != kEndStep) {
+                    const int parts = ((mk[0][0] | mk[0][1] | mk[1][0] | mk[1][1]) != 0ull ? 1 : 0) + ((mk[2][0] | mk[2][1] | mk[3][0] | mk[3][1]) != 0ull ? 1 : 0);
+                    atomicAdd(&g_step_stats[(kind == kGatherStep ? 2 : 0) + (width == 128 ? 0 : 1)], (unsigned long long)parts);
+                    int live = 0;
+                    for (int r = 0; r < 4; ++r) live += __popcll(mk[r][0]) + __popcll(mk[r][1]);
+                    atomicAdd(&g_step_stats[4], (unsigned long long)live);      // visible (row block, key) pairs
+                }
+#endif
             }
             return true;
         };
@@ -818,6 +828,11 @@ int make_tmap_bhnd(CUtensorMap* tm, const void* base, int batch, int heads, int 
 }
 
 #ifdef MINF_TIMELINE
+extern "C" int minf_debug_step_stats(unsigned long long* out, int reset) {
+    if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(g_step_stats, z, sizeof(z)); return 0; }
+    cudaMemcpyFromSymbol(out, g_step_stats, 8 * sizeof(unsigned long long));
+    return 0;
+}
 extern "C" int minf_debug_timeline(long long* buf, int block) {
     cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf));
     cudaMemcpyToSymbol(g_timeline_block, &block, sizeof(block));
