@@ -266,10 +266,15 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     TL_DECL
 
-    const int bh_count = a.batch * a.hq;
-    const int item = a.items_per_head - 1 - (int)(blockIdx.x / bh_count);   // latest rows (most work) first
-    const int bh = (int)(blockIdx.x % bh_count);
-    const int b = bh / a.hq, h = bh % a.hq;
+    // Block order: one KV head at a time (its query heads and all their items, latest rows = most
+    // work first), so that the CTAs in flight stream the same K/V and find it in L2; the K and V
+    // of one KV head at 131072 tokens are 64 MB, half of L2.
+    const int group = a.hq / a.hkv;
+    const int per_kv = a.items_per_head * group;
+    const int kv_slot = (int)(blockIdx.x / per_kv), rem = (int)(blockIdx.x % per_kv);
+    const int item = a.items_per_head - 1 - rem / group;
+    const int b = kv_slot / a.hkv, h = (kv_slot % a.hkv) * group + rem % group;
+    const int bh = b * a.hq + h;
     const int hk = h / (a.hq / a.hkv);
     const int rb_loc0 = item * 4;                   // first row block of the item inside the local queries
     const int lrow0 = rb_loc0 * 64;                 // first local query row
