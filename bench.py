@@ -45,11 +45,46 @@ WORKLOADS = {
     "llama3_8b_8k_vs": (8192, 32, 8, 1000, 6096),
     "llama3_8b_1m_vs": (1048576, 32, 8, 1000, 6096),
 }
+# per-head mix of the three patterns (seeded): A-shape(128, 4096) / vertical-slash(1000, 6096) / block-sparse top-100
+MIXED_WORKLOADS = {
+    "qwen25_7b_256k_mixed": (262144, 28, 4, 1000, 6096),
+}
+WORKLOADS.update(MIXED_WORKLOADS)
+A_SHAPE = (128, 4096)
+
+
+def mixed_pattern_table(hq: int, vsize: int, ssize: int, seed: int = 3):
+    g = torch.Generator().manual_seed(seed)
+    kinds = torch.randint(0, 3, (hq,), generator=g).tolist()
+    table = {}
+    for h, kd in enumerate(kinds):
+        table[str(h)] = (["stream_llm", A_SHAPE[0], A_SHAPE[1], 1.0] if kd == 0 else
+                         ["vertical_and_slash", vsize, ssize, 1.0] if kd == 1 else ["block_sparse", 100, 0, 1.0])
+    return table, kinds
+
+
+def a_shape_tiles(n: int, n_init: int, n_local: int) -> int:
+    """64x64 tiles of one A-shape head: window tiles of every row block plus the sink tiles of the
+    row blocks that reach past the window (the algorithmic count; masked-out sink tiles excluded)."""
+    total = 0
+    for m in range((n + 63) // 64):
+        lo = max(64 * m - n_local + 1, 0) // 64
+        total += m - lo + 1
+        if 64 * m + 63 >= n_local:
+            total += (n_init + 63) // 64
+    return total
+
+
 # with more than one GPU the sequence is sharded over the ranks (zigzag ring); tokens in total
 RING_WORKLOADS = {
     "llama3_8b_1m_vs_ring": (1048576, 32, 8, 1000, 6096),
     "llama3_8b_256k_vs_ring": (262144, 32, 8, 1000, 6096),
 }
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn_fwd_kernel launch, from one-pass ncu
+# captures of the workload itself (the figures and commands are in profiles/); other workloads: not captured
+NCU_TRAFFIC_BYTES = {"llama3_8b_128k_vs": 2.92e9 + 1.04e9, "llama3_8b_32k_vs": 1.94e9 + 0.236e9}
 
 
 def measured_peaks():
@@ -168,8 +203,11 @@ def run_gpu_arm(args, wl):
 
     from minference_b200 import _cabi
     from minference_b200.cuda import set_status_checks
-    from minference_b200.modules.minference_forward import minference_prefill_forward, vertical_slash_estimate
+    from minference_b200.modules.minference_forward import (BLOCK_SPARSE_TOPK, LayerPattern, build_vertical_slash_plan_into,
+                                                            minference_prefill_forward, vertical_slash_estimate)
+    from minference_b200.ops.block_sparse_flash_attention import build_block_sparse_plan
     from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import SparsePlan
     from minference_b200.ops.sparse_forward import sparse_attention_forward
     from minference_b200.synthetic import make_qkv
 
@@ -185,8 +223,16 @@ def run_gpu_arm(args, wl):
     set_status_checks(False)    # status words are read once after the timed region instead
 
     q, k, v = make_qkv(n, hq, hkv, seed=rank, dtype=torch.bfloat16, device=dev)
-    cfg = {"attn_forward_config": {"best_pattern": [{str(h): ["vertical_and_slash", vsize, ssize, 1.0] for h in range(hq)}]},
-           "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
+    mixed = wl in MIXED_WORKLOADS
+    if mixed:
+        table, kinds = mixed_pattern_table(hq, vsize, ssize)
+        pat = LayerPattern(table, hq, n, None, dev)
+        mixed_plan = SparsePlan(plan=torch.zeros(_cabi.lib().minf_plan_bytes(1, hq, n, pat.cap_v, pat.cap_s), dtype=torch.uint8, device=dev),
+                                v_idx=None, cap_v=pat.cap_v, cap_s=pat.cap_s, context_size=n, batch=1, heads=hq,
+                                status=_cabi.new_status(dev))
+    else:
+        table = {str(h): ["vertical_and_slash", vsize, ssize, 1.0] for h in range(hq)}
+    cfg = {"attn_forward_config": {"best_pattern": [table]}, "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     attn_events, est_events, plan_events = [], [], []
@@ -195,11 +241,21 @@ def run_gpu_arm(args, wl):
     def step_resident(record: bool):
         e0, e1, e2, e3 = ev(), ev(), ev(), ev()
         e0.record()
-        v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, vsize, ssize)
-        e1.record()
-        plan = build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)
-        e2.record()
-        out = sparse_attention_forward(q, k, v, plan)
+        if mixed:       # the same calls minference_prefill_forward makes, with events between them
+            plan = mixed_plan
+            v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, pat.vertical_size, pat.slash_size,
+                                                                 cap_v=pat.cap_v, cap_s=pat.cap_s)
+            e1.record()
+            plan.v_idx = build_vertical_slash_plan_into(plan, v_idx, s_idx, nnz_v, nnz_s)
+            build_block_sparse_plan(q, k, BLOCK_SPARSE_TOPK, plan=plan, head_select=pat.block_select)
+            e2.record()
+            out = sparse_attention_forward(q, k, v, plan, head_mode=pat.head_mode, head_param=pat.head_param)
+        else:
+            v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, vsize, ssize)
+            e1.record()
+            plan = build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)
+            e2.record()
+            out = sparse_attention_forward(q, k, v, plan)
         e3.record()
         if record:
             est_events.append((e0, e1)); plan_events.append((e1, e2)); attn_events.append((e2, e3))
@@ -228,7 +284,9 @@ def run_gpu_arm(args, wl):
     status = plan.status.tolist()
     if status[0] != 0 or status[1] != 0:
         raise SystemExit(f"device status {status}: the kernels reported an error")
-    tiles = plan.count_tiles()
+    tiles = plan.count_tiles()      # A-shape heads have empty (zeroed) plan slots
+    if mixed:
+        tiles += kinds.count(0) * a_shape_tiles(n, *A_SHAPE)
     attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
     est_ms = sum(a.elapsed_time(b) for a, b in est_events) / len(est_events)
     plan_ms = sum(a.elapsed_time(b) for a, b in plan_events) / len(plan_events)
@@ -270,6 +328,8 @@ def run_gpu_arm(args, wl):
         peaks = measured_peaks()
         achieved = tiles * FLOP_PER_TILE / (attn_ms * 1e-3) / 1e12
         cpu_tf, cpu_desc = cpu_sample(n, hq, hkv, vsize, ssize, seed=0, budget_s=12.0)
+        if mixed:
+            cpu_desc = "vertical-slash heads only; " + cpu_desc
         rows = (n + 63) // 64
         out = {
             "metric": "sparse_prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -277,17 +337,20 @@ def run_gpu_arm(args, wl):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wl, "tokens": n, "q_heads": hq, "kv_heads": hkv, "head_dim": 128, "vertical": vsize,
                        "slash": ssize, "last_q": 64, "l2": "inputs_exceed_l2", "replicas": world,
+                       **({"head_patterns": {"a_shape": kinds.count(0), "vertical_slash": kinds.count(1),
+                                             "block_sparse": kinds.count(2)}} if mixed else {}),
                        "tiles_per_layer": tiles, "fraction_of_causal_tiles": tiles / (hq * rows * (rows + 1) / 2),
                        "dense_equivalent_tflops": 4.0 * (n * n / 2) * 128 * hq * world / (ms_per_step * 1e-3) / 1e12,
                        "ms_estimator": est_ms, "ms_plan": plan_ms, "ms_attention": attn_ms},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (q, k, v)),
                     "d2h_bytes_per_step": q.numel() * q.element_size(), "max_abs_vs_resident_last_row": parity_probe},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": (7 if mixed else 5) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "sparse_attn_fwd_kernel", "achieved": achieved,
                          "peak": peaks["sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["sustained"],
                          "peak_kind": f"bf16 dense sustained, of {peaks['source']}", "frac_of_burst": achieved / peaks["burst"],
-                         "traffic": None},
+                         "traffic": NCU_TRAFFIC_BYTES.get(wl), "traffic_unit": "bytes per launch (ncu)",
+                         "algorithmic_bytes": (2 * hq + 2 * hkv) * n * 128 * 2},
             "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                              "sample": cpu_desc},
             "clocks": clocks,
