@@ -463,17 +463,88 @@ def run_ring_arm(args, wl):
     dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ whole-model prefill (TTFT)
+
+TTFT_WORKLOADS = {
+    # name: (tokens, layers) of the Llama-3-8B architecture with seeded random weights and seeded per-head patterns
+    "llama3_8b_512k_ttft": (524288, 32),
+    "llama3_8b_128k_ttft": (131072, 32),
+    "llama3_8b_32k_ttft_4layers": (32768, 4),
+}
+
+
+def run_ttft_arm(args, wl):
+    """One ``use_cache=False``-style forward of the whole network over one long prompt; a step is
+    one prefill, timed with CUDA events, token ids copied from pinned host memory inside the timed
+    region and the last token's logits copied back."""
+    from minference_b200 import _cabi
+    from minference_b200.cuda import set_status_checks
+    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables
+
+    n, layers = TTFT_WORKLOADS[wl]
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    _cabi.lib()
+    set_status_checks(False)
+    shape = LlamaShape(layers=layers)
+    model = LlamaPrefill(shape, dev, seed=0)
+    tables = seeded_pattern_tables(shape, seed=0)
+    cfg = {"starting_layer": 0, "best_pattern": tables}
+    ids_host = torch.randint(0, shape.vocab, (n,), generator=torch.Generator().manual_seed(0)).pin_memory()
+    logits_host = torch.empty(shape.vocab, dtype=torch.float32).pin_memory()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def step():
+        ids = ids_host.to(dev, non_blocking=True)
+        logits_host.copy_(model.prefill(ids, cfg), non_blocking=True)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    t0, t1 = ev(), ev()
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ttft_s = t0.elapsed_time(t1) / args.steps / 1e3
+    kinds = [t[0] for layer in tables for t in layer.values()]
+    dense_flop = 2.0 * n * layers * (shape.hidden * (shape.q_heads + 2 * shape.kv_heads) * 128 + shape.q_heads * 128 * shape.hidden
+                                     + 3 * shape.hidden * shape.ffn)
+    out = {
+        "metric": "ttft_s", "value": ttft_s, "unit": "s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ttft_s * 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": wl, "tokens": n, "layers": layers, "hidden": shape.hidden, "q_heads": shape.q_heads,
+                   "kv_heads": shape.kv_heads, "ffn": shape.ffn, "vocab": shape.vocab, "weights": "random init, seed 0",
+                   "head_patterns": {kd: kinds.count(kd) for kd in sorted(set(kinds))},
+                   "dense_gemm_pflop": dense_flop / 1e15, "dense_parts": "torch.matmul (cuBLAS), chunked over 16384 tokens",
+                   "tokens_per_s": n / ttft_s, "finite_logits": bool(torch.isfinite(logits_host).all())},
+        "e2e": {"value": ttft_s, "unit": "s", "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size(),
+                "d2h_bytes_per_step": logits_host.numel() * 4},
+        "gpu_launches": None, "roofline": None, "cpu_baseline": None, "clocks": clocks,
+    }
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(TTFT_WORKLOADS))
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload is None:
         args.workload = "llama3_8b_128k_vs" if world == 1 else "llama3_8b_1m_vs_ring"
+    if args.workload in TTFT_WORKLOADS:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the whole-model prefill has no CPU arm; the attention workloads do"}))
+            return
+        return run_ttft_arm(args, args.workload)
     if args.impl == "reference":
         # the CPU arm times the same per-tile work; for a ring workload it uses the single-GPU shape of that length
         wl = args.workload if args.workload in WORKLOADS else args.workload.replace("_ring", "")
