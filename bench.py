@@ -48,6 +48,7 @@ WORKLOADS = {
 # per-head mix of the three patterns (seeded): A-shape(128, 4096) / vertical-slash(1000, 6096) / block-sparse top-100
 MIXED_WORKLOADS = {
     "qwen25_7b_256k_mixed": (262144, 28, 4, 1000, 6096),
+    "llama3_8b_512k_mixed": (524288, 32, 8, 1000, 6096),
 }
 WORKLOADS.update(MIXED_WORKLOADS)
 A_SHAPE = (128, 4096)
