@@ -471,63 +471,98 @@ TTFT_WORKLOADS = {
     "llama3_8b_512k_ttft": (524288, 32),
     "llama3_8b_128k_ttft": (131072, 32),
     "llama3_8b_32k_ttft_4layers": (32768, 4),
+    # vertical-slash on every head; with N > 1 ranks the prompt is sequence-sharded (zigzag ring)
+    "llama3_8b_1m_ttft_vs": (1048576, 32),
+    "llama3_8b_256k_ttft_vs_4layers": (262144, 4),
 }
 
 
 def run_ttft_arm(args, wl):
     """One ``use_cache=False``-style forward of the whole network over one long prompt; a step is
     one prefill, timed with CUDA events, token ids copied from pinned host memory inside the timed
-    region and the last token's logits copied back."""
+    region and the last token's logits copied back.  Under torchrun the prompt is sharded over the
+    ranks in zigzag chunks: dense parts are token-parallel, attention is the vertical-slash ring."""
+    import torch.distributed as dist
+
     from minference_b200 import _cabi
     from minference_b200.cuda import set_status_checks
-    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables
+    from minference_b200.dist import ring
+    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables, zigzag_positions
 
     n, layers = TTFT_WORKLOADS[wl]
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     _cabi.lib()
     set_status_checks(False)
     shape = LlamaShape(layers=layers)
-    model = LlamaPrefill(shape, dev, seed=0)
-    tables = seeded_pattern_tables(shape, seed=0)
+    model = LlamaPrefill(shape, dev, seed=0)            # same seed: identical weights on every rank
+    vs_only = wl.endswith("_vs") or "_vs_" in wl
+    if world > 1 and not vs_only:
+        raise SystemExit("only the vertical-slash TTFT workloads are sequence-sharded")
+    tables = seeded_pattern_tables(shape, seed=0, kinds=("vertical_and_slash",) if vs_only else
+                                   ("stream_llm", "vertical_and_slash", "block_sparse"))
     cfg = {"starting_layer": 0, "best_pattern": tables}
-    ids_host = torch.randint(0, shape.vocab, (n,), generator=torch.Generator().manual_seed(0)).pin_memory()
+    ids_all = torch.randint(0, shape.vocab, (n,), generator=torch.Generator().manual_seed(0))
+    positions = zigzag_positions(n, rank, world, dev) if world > 1 else None
+    ids_host = (ids_all[positions.cpu()] if world > 1 else ids_all).pin_memory()
     logits_host = torch.empty(shape.vocab, dtype=torch.float32).pin_memory()
+    attention = (lambda q, k, v, li: ring.ring_vertical_slash_attention(q, k, v, n, 1000, 6096)) if world > 1 else None
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     def step():
         ids = ids_host.to(dev, non_blocking=True)
-        logits_host.copy_(model.prefill(ids, cfg), non_blocking=True)
+        logits = model.prefill(ids, cfg, positions=positions, attention=attention)
+        if rank == 0:       # the prompt's last token is rank 0's last token
+            logits_host.copy_(logits, non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
     t0, t1 = ev(), ev()
     t0.record()
     for _ in range(args.steps):
         step()
     t1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ttft_s = t0.elapsed_time(t1) / args.steps / 1e3
-    kinds = [t[0] for layer in tables for t in layer.values()]
-    dense_flop = 2.0 * n * layers * (shape.hidden * (shape.q_heads + 2 * shape.kv_heads) * 128 + shape.q_heads * 128 * shape.hidden
-                                     + 3 * shape.hidden * shape.ffn)
-    out = {
-        "metric": "ttft_s", "value": ttft_s, "unit": "s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ttft_s * 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": wl, "tokens": n, "layers": layers, "hidden": shape.hidden, "q_heads": shape.q_heads,
-                   "kv_heads": shape.kv_heads, "ffn": shape.ffn, "vocab": shape.vocab, "weights": "random init, seed 0",
-                   "head_patterns": {kd: kinds.count(kd) for kd in sorted(set(kinds))},
-                   "dense_gemm_pflop": dense_flop / 1e15, "dense_parts": "torch.matmul (cuBLAS), chunked over 16384 tokens",
-                   "tokens_per_s": n / ttft_s, "finite_logits": bool(torch.isfinite(logits_host).all())},
-        "e2e": {"value": ttft_s, "unit": "s", "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size(),
-                "d2h_bytes_per_step": logits_host.numel() * 4},
-        "gpu_launches": None, "roofline": None, "cpu_baseline": None, "clocks": clocks,
-    }
-    print(json.dumps(out))
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ttft_s = t.item() / args.steps / 1e3
+    if rank == 0:
+        kinds = [e[0] for layer in tables for e in layer.values()]
+        dense_flop = 2.0 * n * layers * (shape.hidden * (shape.q_heads + 2 * shape.kv_heads) * 128 + shape.q_heads * 128 * shape.hidden
+                                         + 3 * shape.hidden * shape.ffn)
+        out = {
+            "metric": "ttft_s", "value": ttft_s, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ttft_s * 1e3, "higher_is_better": False, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl, "tokens": n, "tokens_per_gpu": n // world, "layers": layers, "hidden": shape.hidden,
+                       "q_heads": shape.q_heads, "kv_heads": shape.kv_heads, "ffn": shape.ffn, "vocab": shape.vocab,
+                       "weights": "random init, seed 0",
+                       "head_patterns": {kd: kinds.count(kd) for kd in sorted(set(kinds))},
+                       "parallelism": f"zigzag sequence split over {world} ranks, ring attention" if world > 1 else "one GPU",
+                       "dense_gemm_pflop": dense_flop / 1e15, "dense_parts": "torch.matmul (cuBLAS), chunked over 16384 tokens",
+                       "tokens_per_s": n / ttft_s, "finite_logits": bool(torch.isfinite(logits_host).all())},
+            "e2e": {"value": ttft_s, "unit": "s", "h2d_bytes_per_step": world * ids_host.numel() * ids_host.element_size(),
+                    "d2h_bytes_per_step": logits_host.numel() * 4},
+            "gpu_launches": None, "roofline": None, "cpu_baseline": None, "clocks": clocks,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():

@@ -111,6 +111,15 @@ class LlamaPrefill:
         return (self._rms(x[-1:], self.final_norm) @ self.lm_head)[0].float()
 
 
+def zigzag_positions(n_ctx: int, rank: int, world: int, device=None) -> torch.Tensor:
+    """Positions in the prompt of the tokens rank ``rank`` owns under the zigzag sequence split
+    (chunks ``rank`` and ``2*world-1-rank``); the prompt's last token is the last one of rank 0."""
+    from .dist.ring import chunk_size, owned_chunks
+
+    c = chunk_size(n_ctx, world)
+    return torch.cat([torch.arange(ch * c, (ch + 1) * c, device=device) for ch in owned_chunks(rank, world)])
+
+
 def _rope_at(positions: torch.Tensor, dim: int, theta: float):
     inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, device=positions.device, dtype=torch.float32) / dim))
     freqs = torch.outer(positions.float(), inv_freq)

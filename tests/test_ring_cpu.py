@@ -113,3 +113,52 @@ def test_merge_partial_matches_joint_softmax():
         lse = torch.logsumexp(part, -1) / np.log(2.0)
         ring.merge_partial(acc_o, acc_l, o, lse)
     assert (acc_o - ref).abs().max() < 1e-5
+
+
+def _dense_window(q, k, v, qi, q_pos0, kv_pos0):
+    """Plain causal attention of one (query chunk, key chunk) pair at global positions + base-2 lse."""
+    B, H, C, D = q.shape
+    rep = H // k.shape[1]
+    kk, vv = k.repeat_interleave(rep, 1).float(), v.repeat_interleave(rep, 1).float()
+    s = (q.float() @ kk.transpose(-1, -2)) * D ** -0.5
+    rows = q_pos0 + torch.arange(C)[:, None]
+    cols = kv_pos0 + torch.arange(k.shape[2])[None, :]
+    s = s.masked_fill(cols > rows, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+    return (p @ vv).to(q.dtype), lse / np.log(2.0)
+
+
+def _runner_worker(rank, world, port, n, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from minference_b200.prefill_runner import (LlamaPrefill, LlamaShape, dense_reference_logits,
+                                                    zigzag_positions)
+
+        shape = LlamaShape(layers=2, hidden=256, q_heads=2, kv_heads=1, head_dim=128, ffn=512, vocab=500)
+        model = LlamaPrefill(shape, "cpu", seed=3, dtype=torch.float32, init_std=0.05)     # same weights on every rank
+        ids = torch.randint(0, shape.vocab, (n,), generator=torch.Generator().manual_seed(4))
+        pos = zigzag_positions(n, rank, world)
+        logits = model.prefill(ids[pos], None, chunk=200, positions=pos,
+                               attention=lambda q, k, v, li: ring.ring_attention(q, k, v, n, _dense_window))
+        if rank == 0:
+            result.put(float((logits - dense_reference_logits(model, ids)).abs().max()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_sharded_whole_model_prefill_on_gloo_ranks():
+    """Token-parallel dense parts + ring attention reproduce the unsharded network's last-token logits."""
+    world, n = 2, 256 * 4
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_runner_worker, args=(r, world, port, n, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+        assert p.exitcode == 0
+    assert result.get(timeout=10) < 1e-3
