@@ -37,6 +37,21 @@ def main():
         # the index sets may differ in a few near-ties (different summation order of the statistics)
         print(f"ring vs whole-sequence: max {d.max().item():.3e} mean {d.mean().item():.3e}")
         ok = d.mean().item() < 2e-3 and torch.isfinite(merged).all().item()
+    # whole network, sequence-sharded, against the same network on one GPU (both through the CUDA kernels)
+    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables, zigzag_positions
+
+    shape = LlamaShape(layers=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=1000)
+    model = LlamaPrefill(shape, dev, seed=1, init_std=0.05)
+    ids = torch.randint(0, shape.vocab, (n,), generator=torch.Generator().manual_seed(2))
+    pos = zigzag_positions(n, rank, world, dev)
+    logits = model.prefill(ids[pos.cpu()], None, chunk=1024, positions=pos,
+                           attention=lambda q_, k_, v_, li: ring.ring_vertical_slash_attention(q_, k_, v_, n, 200, 600))
+    if rank == 0:
+        tables = seeded_pattern_tables(shape, seed=0, vertical=200, slash=600, kinds=("vertical_and_slash",))
+        single = model.prefill(ids, {"starting_layer": 0, "best_pattern": tables}, chunk=1024)
+        dl = (logits - single).abs().max().item()
+        print(f"sharded vs single-GPU logits: max {dl:.3e} (scale {single.abs().max().item():.3e})")
+        ok = ok and dl <= 3e-2 * single.abs().max().item() + 1e-3 and torch.isfinite(logits).all().item()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, src=0)
     dist.destroy_process_group()
