@@ -312,7 +312,10 @@ def run_gpu_arm(args, wl):
     s1.record()
     barrier()
     e2e_ms = s0.elapsed_time(s1) / e2e_steps
+    tiles_box["plan"].status[2:].zero_()        # the mixed workload reuses one status buffer for every launch
     parity_probe = float((ho[0, 0, -1].float() - step_resident(False)[0, 0, -1].float().cpu()).abs().max())
+    st = tiles_box["plan"].status.tolist()      # words 2-3: tile equivalents the kernel sent to the tensor pipe in that launch
+    issued_tiles = (st[2] & 0xFFFFFFFF) | ((st[3] & 0xFFFFFFFF) << 32)
 
     times = torch.tensor([total_ms, e2e_ms, attn_ms], dtype=torch.float64, device=dev)
     tile_sum = torch.tensor([float(tiles)], dtype=torch.float64, device=dev)
@@ -342,7 +345,8 @@ def run_gpu_arm(args, wl):
                                              "block_sparse": kinds.count(2)}} if mixed else {}),
                        "tiles_per_layer": tiles, "fraction_of_causal_tiles": tiles / (hq * rows * (rows + 1) / 2),
                        "dense_equivalent_tflops": 4.0 * (n * n / 2) * 128 * hq * world / (ms_per_step * 1e-3) / 1e12,
-                       "ms_estimator": est_ms, "ms_plan": plan_ms, "ms_attention": attn_ms},
+                       "ms_estimator": est_ms, "ms_plan": plan_ms, "ms_attention": attn_ms,
+                       "issued_over_reference_tiles": issued_tiles / max(tiles, 1)},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (q, k, v)),
                     "d2h_bytes_per_step": q.numel() * q.element_size(), "max_abs_vs_resident_last_row": parity_probe},

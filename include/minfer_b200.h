@@ -33,8 +33,8 @@ extern "C" {
 #define MINF_STATUS_WORDS 4
 #define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan */
 #define MINF_ST_NO_SLASH 1   /* number of row blocks whose slash list has no offset < end row */
-#define MINF_ST_AUX0 2
-#define MINF_ST_AUX1 3
+#define MINF_ST_AUX0 2        /* words 2-3, read as one uint64: 64x64 tile equivalents the attention kernel sent  */
+#define MINF_ST_AUX1 3        /* to the tensor pipe (its 128-row x 64/128-key steps), summed over launches         */
 
 /* per-head attention pattern, values of head_mode[] */
 #define MINF_MODE_PLAN 0     /* vertical-slash or block-sparse: tiles and columns come from the plan */

@@ -331,6 +331,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             }
         }
         int step = 0;
+        unsigned issued = 0;           // 64x64 tile equivalents this CTA sends to the tensor pipe
         bool ok = true;
         auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
             const int s = idx % ring, use = idx / ring;
@@ -341,9 +342,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (!wait_use(ctl->m_empty, kNM, step)) return false;
             if (lane == 0) {
                 Step& st = ctl->step[step % kNM];
-                *reinterpret_cast<int4*>(&st) = make_int4(kind, t, width,
-                    ((mk[0][0] | mk[0][1] | mk[1][0] | mk[1][1]) != 0ull ? 1 : 0) |
-                    ((mk[2][0] | mk[2][1] | mk[3][0] | mk[3][1]) != 0ull ? 2 : 0));
+                const int parts = ((mk[0][0] | mk[0][1] | mk[1][0] | mk[1][1]) != 0ull ? 1 : 0) |
+                                  ((mk[2][0] | mk[2][1] | mk[3][0] | mk[3][1]) != 0ull ? 2 : 0);
+                *reinterpret_cast<int4*>(&st) = make_int4(kind, t, width, parts);
+                issued += (unsigned)(__popc(parts) * (width >> 5));     // a slot is two row blocks tall
 #pragma unroll
                 for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
                 mbar_arrive(bar(&ctl->m_full[step % kNM]));
@@ -574,6 +576,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
                 mbar_arrive(bar(&ctl->k_full[step % kNK]));
         }
+        if (lane == 0 && issued)
+            atomicAdd(reinterpret_cast<unsigned long long*>(a.status + MINF_ST_AUX0), (unsigned long long)issued);
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");

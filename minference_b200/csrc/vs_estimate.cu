@@ -36,7 +36,8 @@ constexpr uint32_t kEstQBytes = 128 * 256;
 constexpr uint32_t kEstKBytes = 128 * 256;
 constexpr uint32_t kEstPOff = kEstQBytes + 2 * kEstKBytes;           // 98304
 constexpr uint32_t kEstPBytes = 128 * kEstPitch * 4;                 // 66048
-constexpr uint32_t kEstCtlOff = kEstPOff + kEstPBytes;
+// pass 1 keeps no probability tile, so two of its CTAs fit one SM
+template <int PASS> constexpr uint32_t est_ctl_off() { return PASS == 1 ? kEstPOff : kEstPOff + kEstPBytes; }
 
 struct EstControl {
     unsigned long long q_full;
@@ -55,20 +56,36 @@ struct EstArgs {
     float* vertical;                 // [batch*hq][n_ctx]
     float* slash;                    // [batch*hq][n_ctx], indexed by diagonal offset
     float inv_sqrt_d_div;            // sqrt(d): logits are divided by it
+    float rcp_sqrt_d;                // its reciprocal, for the refined multiply that replaces the division
     int32_t* status;
 };
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// x / d correctly rounded from a reciprocal and one Newton step on the exact remainder (no MUFU,
+// three FMA-pipe instructions instead of the division sequence).
+__device__ __forceinline__ float div_refined(float x, float d, float rcp) {
+    const float q = x * rcp;
+    return fmaf(fmaf(-q, d, x), rcp, q);
+}
+// The reference's logits: the bf16 GEMM output divided by sqrt(d) in fp32 and rounded to bf16 again.
+__device__ __forceinline__ void logits_pair(uint32_t a0, uint32_t a1, float d, float rcp, float& v0, float& v1) {
+    const uint32_t g = pack_bf16x2(__uint_as_float(a0), __uint_as_float(a1));
+    const uint32_t r = pack_bf16x2(div_refined(__uint_as_float(g << 16), d, rcp),
+                                   div_refined(__uint_as_float(g & 0xffff0000u), d, rcp));
+    v0 = __uint_as_float(r << 16);
+    v1 = __uint_as_float(r & 0xffff0000u);
+}
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 template <int PASS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, PASS == 1 ? 2 : 1)
 vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const EstArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    EstControl* ctl = reinterpret_cast<EstControl*>(smem + kEstCtlOff);
+    EstControl* ctl = reinterpret_cast<EstControl*>(smem + est_ctl_off<PASS>());
     float* ptile = reinterpret_cast<float*>(smem + kEstPOff);
     const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -181,6 +198,8 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ok = mbar_wait(bar(&ctl->s_full[s]), use & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            // only the tiles that reach the last queries' diagonal or the end of the keys need masks
+            const bool plain = row_ok && c0 + kEstTileN - 1 <= q_pos0 && l0 + kEstTileN <= a.n_k;
 #pragma unroll 1
             for (int q4 = 0; q4 < 4; ++q4) {
                 uint32_t xr[32];
@@ -188,12 +207,22 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 tmem_wait_ld();
                 float x[32];
                 float mx = -INFINITY;
+                if (plain) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int c = c0 + q4 * 32 + j;
-                    const float v = bf16_round(bf16_round(__uint_as_float(xr[j])) / a.inv_sqrt_d_div);
-                    x[j] = (row_ok && c <= qpos && l0 + q4 * 32 + j < a.n_k) ? v : -INFINITY;
-                    mx = fmaxf(mx, x[j]);
+                    for (int j = 0; j < 32; j += 2) {
+                        logits_pair(xr[j], xr[j + 1], a.inv_sqrt_d_div, a.rcp_sqrt_d, x[j], x[j + 1]);
+                        mx = max3(mx, x[j], x[j + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float v0, v1;
+                        logits_pair(xr[j], xr[j + 1], a.inv_sqrt_d_div, a.rcp_sqrt_d, v0, v1);
+                        const int c = c0 + q4 * 32 + j;
+                        x[j] = (row_ok && c <= qpos && l0 + q4 * 32 + j < a.n_k) ? v0 : -INFINITY;
+                        x[j + 1] = (row_ok && c + 1 <= qpos && l0 + q4 * 32 + j + 1 < a.n_k) ? v1 : -INFINITY;
+                        mx = max3(mx, x[j], x[j + 1]);
+                    }
                 }
                 if (PASS == 1) {
                     if (mx > row_m) {
@@ -201,13 +230,17 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         row_m = mx;
                     }
                     if (row_m > -INFINITY) {
+                        const float neg = -row_m * kLog2e;
+                        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) row_l += exp2f((x[j] - row_m) * kLog2e);
+                        for (int j = 0; j < 32; ++j) part[j & 3] += exp2f(fmaf(x[j], kLog2e, neg));
+                        row_l += (part[0] + part[1]) + (part[2] + part[3]);
                     }
                 } else {
+                    const float neg = -row_m * kLog2e;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        ptile[r * kEstPitch + q4 * 32 + j] = row_ok ? exp2f((x[j] - row_m) * kLog2e) * inv_l : 0.f;
+                        ptile[r * kEstPitch + q4 * 32 + j] = row_ok ? exp2f(fmaf(x[j], kLog2e, neg)) * inv_l : 0.f;
                 }
             }
             tc_fence_before();
@@ -436,13 +469,14 @@ extern "C" int minf_vs_scores_pass(
     a.stats = static_cast<float2*>(stats);
     a.vertical = vertical_scores; a.slash = slash_scores;
     a.inv_sqrt_d_div = sqrtf((float)head_dim);
+    a.rcp_sqrt_d = 1.0f / a.inv_sqrt_d_div;
     a.status = status;
     CUtensorMap tq, tk;
     int rc;
     if ((rc = make_tmap_bhnd(&tq, q_last, batch, hq, a.last_q, q_strides, 64, "q_last"))) return rc;
     if ((rc = make_tmap_bhnd(&tk, k, batch, hkv, n_k, k_strides, 128, "k"))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = kEstCtlOff + sizeof(EstControl);
+    const size_t smem = (pass == 1 ? est_ctl_off<1>() : est_ctl_off<2>()) + sizeof(EstControl);
     dim3 grid(a.chunks, hkv * a.pairs_per_group, batch);
     if (pass == 1) {
         MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -59,7 +59,7 @@ def test_windowed_kernel_pairs_merge_to_full_attention(dev, world, n, kind):
                                                dv[:, :, kc * c:(kc + 1) * c], n, qc * c, kc * c, plan, dvs,
                                                dss.shape[2], status)
                 ring.merge_partial(acc_o, acc_l, o, lse)
-            assert status.tolist() == [0, 0, 0, 0]
+            assert status.tolist()[:2] == [0, 0]       # words 2-3 count the tiles sent to the tensor pipe
             outs.append(acc_o)
         parts.append(torch.cat(outs, dim=2))
     merged = ring.zigzag_merge(parts, world)
