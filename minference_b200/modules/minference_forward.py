@@ -118,16 +118,20 @@ def minference_prefill_forward(query_states, key_states, value_states, prefill_k
     count (already repeated, as the reference's caller passes them) or the KV head count.
     """
     cfg = prefill_kwargs["attn_forward_config"]
-    if cfg.get("is_search", False):
-        raise NotImplementedError("offline pattern search is not part of this library")
     starting_layer = cfg.get("starting_layer", 0)
     layer_idx = prefill_kwargs["layer_idx"]
     _cabi.require_cuda(query_states, key_states, value_states)
     B, H, N, D = query_states.shape
     assert B == 1, "the estimator of the reference is defined for batch 1 (as_strided view, :114)"
     dev = query_states.device
+    is_search = cfg.get("is_search", False)
+    if is_search:       # offline search: record this layer's best patterns, run the layer dense (:644-650, :661-666)
+        from .pattern_search import search_and_record
 
-    if layer_idx < starting_layer:          # dense causal layers (:665-666)
+        search_and_record(query_states, key_states, value_states, layer_idx,
+                          prefill_kwargs.get("num_hidden_layers", 0), cfg.get("config_path"))
+
+    if is_search or layer_idx < starting_layer:          # dense causal layers (:665-666)
         mode = torch.full((H,), _cabi.MODE_ASHAPE, dtype=torch.int32, device=dev)
         param = torch.tensor([[0, N]] * H, dtype=torch.int32, device=dev)
         return sparse_attention_forward(query_states, key_states, value_states, None, head_mode=mode, head_param=param)

@@ -37,8 +37,11 @@ def _as_bhnd(t: torch.Tensor) -> torch.Tensor:
 
 
 def sparse_attention_forward(query, key, value, plan: SparsePlan | None, head_mode=None, head_param=None,
-                             sm_scale: float | None = None, out: torch.Tensor | None = None):
-    """Launch ``minf_sparse_attention_fwd`` on the current stream and return ``[B,H,N,D]``."""
+                             sm_scale: float | None = None, out: torch.Tensor | None = None, return_lse: bool = False):
+    """Launch ``minf_sparse_attention_fwd`` on the current stream and return ``[B,H,N,D]``.
+
+    ``return_lse=True`` also returns the per-row base-2 log-sum-exp of the scaled logits over the
+    keys the pattern selects, ``[B,H,N]`` fp32 (-inf for a row with no visible key)."""
     if query.dtype != torch.bfloat16:
         raise _cabi.MInferB200Error(f"bf16 inputs required (got {query.dtype}); there is no other kernel")
     if not (key.dtype == value.dtype == query.dtype):
@@ -52,6 +55,21 @@ def sparse_attention_forward(query, key, value, plan: SparsePlan | None, head_mo
         sm_scale = D ** -0.5
     dev = query.device
     status = plan.status if plan is not None else _cabi.new_status(dev)
+    if return_lse:
+        lse = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
+                _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse),
+                _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
+                B, H, Hkv, N, N, 0, N, 0, D, float(sm_scale),
+                _cabi.ptr(head_mode), _cabi.ptr(head_param),
+                _cabi.ptr(plan.plan if plan is not None else None),
+                _cabi.ptr(plan.v_idx if plan is not None else None),
+                plan.cap_v if plan is not None else 0, plan.cap_s if plan is not None else 1,
+                _cabi.ptr(status), _cabi.stream_ptr(dev)))
+        if plan is None:
+            sparse_attention_forward.last_status = status
+        return out, lse
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().minf_sparse_attention_fwd(
             _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out),
