@@ -1,7 +1,8 @@
 """Configuration object of the patch API (mirrors minference/minference_configuration.py:7-111).
 
 Only the attention types that run on this library's kernels are accepted: the dynamic sparse
-prefill ("minference"), the fixed A-shape pattern ("a_shape") and dense causal ("dense").  The
+prefill ("minference", also with ``is_search=True`` for the offline pattern search), the fixed A-shape
+pattern ("a_shape"), A-shape with dense last rows ("tri_shape") and dense causal ("dense").  The
 KV-cache methods of the reference (kv_type other than "dense") are decode-side features outside
 this library.
 """
@@ -12,7 +13,7 @@ from .configs.model2path import MODEL2PATH
 
 class MInferenceConfig:
     MINFERENCE_ATTENTION_TYPES = ["minference"]
-    OTHER_ATTENTION_TYPES = ["dense", "a_shape"]
+    OTHER_ATTENTION_TYPES = ["dense", "a_shape", "tri_shape"]
     KV_TYPES = ["dense"]
 
     def __init__(
@@ -35,8 +36,8 @@ class MInferenceConfig:
             raise ValueError(f"The kv_type {kv_type} you specified is not supported.")
         if kv_cache_cpu:
             raise ValueError("kv_cache_cpu is not supported: the KV tensors must be resident on the GPU")
-        if is_search:
-            raise ValueError("offline pattern search is not part of this library")
+        if is_search and config_path is None:
+            raise ValueError("is_search needs config_path: the file the searched pattern table is written to")
         self.attn_type = attn_type
         self.config_path = self.update_config_path(config_path, model_name)
         self.model_name = model_name

@@ -32,12 +32,17 @@ class MInference:
         model.config.config_path = self.config.config_path
         if self.config.attn_type == "minference":
             # the pattern table is loaded once here (models_patch.py:98-102 of the reference)
-            if "best_pattern" not in self.config.attn_kwargs:
+            if self.config.is_search:
+                # every prefill call searches its layer and appends to config_path; layers run dense meanwhile
+                self.config.attn_kwargs["config_path"] = self.config.config_path
+            elif "best_pattern" not in self.config.attn_kwargs:
                 with open(self.config.config_path, "r") as f:
                     self.config.attn_kwargs["best_pattern"] = json.load(f)
             if self.config.attn_kwargs.get("starting_layer", -1) < 0:
                 self.config.attn_kwargs["starting_layer"] = 0
-        elif self.config.attn_type == "a_shape":
+        elif self.config.attn_type in ("a_shape", "tri_shape"):
             self.config.attn_kwargs.setdefault("n_local", 3968)
             self.config.attn_kwargs.setdefault("n_init", 128)
+            if self.config.attn_type == "tri_shape":
+                self.config.attn_kwargs.setdefault("n_last", 100)
         return new_patch(model, self.config)

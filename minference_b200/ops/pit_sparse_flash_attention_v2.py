@@ -55,3 +55,22 @@ def vertical_slash_sparse_attention(
     if _status_checks_enabled():
         _cabi.raise_on_status(plan.status, "vertical_slash_sparse_attention")
     return out
+
+
+def dilated_sparse_attention(query, key, value, kind: str):
+    """The fixed index sets of the reference's ``dialted`` variants
+    (modules/minference_forward.py:365-379): the first 1024 keys as vertical lines and
+    ``dilated1`` every second of the 8192 nearest diagonals, ``dilated2`` the 2048 nearest
+    diagonals plus every second of the next 4096."""
+    n = query.shape[2]
+    dev = query.device
+    v_idx = torch.arange(0, min(1024, n), device=dev)[None, None, :].expand(query.shape[0], query.shape[1], -1)
+    pos = torch.arange(0, n, device=dev)
+    if kind == "dilated1":
+        pos = pos[-8192::2]
+    elif kind == "dilated2":
+        pos = torch.cat([pos[-2048:], pos[-6144:-2048:2]], 0)
+    else:
+        raise KeyError(kind)
+    s_idx = ((n - 1) - pos)[None, None, :].expand(query.shape[0], query.shape[1], -1)
+    return vertical_slash_sparse_attention(query, key, value, v_idx, s_idx)

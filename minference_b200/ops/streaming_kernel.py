@@ -33,3 +33,38 @@ def a_shape_kernel(q, k, v, config):
     n_init = config["attn_forward_config"].get("n_init", 128)
     n_local = config["attn_forward_config"].get("n_local", 3968)
     return streaming_forward(q, k, v, n_init, n_local)
+
+
+def tri_shape_kernel(q, k, v, config):
+    """A-shape attention for all rows but the last ``n_last``, which attend to every earlier key
+    (streaming_kernel.py:820-833 of the reference: the A-shape part sees the sequence cut before
+    the last rows; the last rows are plain causal attention).
+
+    Two launches of the same kernel: the A-shape rows, then a dense window that starts at the
+    256-row boundary at or before the first of the last rows (the kernel's query windows start on
+    256-row boundaries); only the last ``n_last`` rows of that window are kept.
+    """
+    _cabi.require_cuda(q, k, v)
+    B, H, N, D = q.shape
+    n_last = min(config["attn_forward_config"].get("n_last", 100), N - 1)
+    cut = N - n_last
+    y1 = a_shape_kernel(q[:, :, :cut], k[:, :, :cut], v[:, :, :cut], config)
+    q0 = cut // 256 * 256
+    dev = q.device
+    mode = torch.full((H,), _cabi.MODE_ASHAPE, dtype=torch.int32, device=dev)
+    param = torch.tensor([[0, N]] * H, dtype=torch.int32, device=dev)          # window of N keys = dense causal
+    qw = q[:, :, q0:]
+    qw = qw if (qw.stride(3) == 1 and qw.data_ptr() % 16 == 0) else qw.contiguous()
+    kk = k if k.stride(3) == 1 else k.contiguous()
+    vv = v if v.stride(3) == 1 else v.contiguous()
+    out = torch.empty((B, H, N - q0, D), dtype=q.dtype, device=dev)
+    status = _cabi.new_status(dev)
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
+            _cabi.ptr(qw), _cabi.ptr(kk), _cabi.ptr(vv), _cabi.ptr(out), None,
+            _cabi.strides3(qw), _cabi.strides3(kk), _cabi.strides3(vv), _cabi.strides3(out),
+            B, H, kk.shape[1], N, N - q0, q0, N, 0, D, float(D ** -0.5),
+            _cabi.ptr(mode), _cabi.ptr(param), None, None, 0, 1, _cabi.ptr(status), _cabi.stream_ptr(dev)))
+    if _status_checks_enabled():
+        _cabi.raise_on_status(status, "tri_shape_kernel")
+    return torch.cat([y1, out[:, :, cut - q0:]], dim=2)

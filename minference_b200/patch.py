@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from .modules.minference_forward import minference_prefill_forward
-from .ops.streaming_kernel import a_shape_kernel
+from .ops.streaming_kernel import a_shape_kernel, tri_shape_kernel
 
 ATTN_NAME = "minference_b200"
 
@@ -35,6 +35,8 @@ def _make_attention_function(config):
                                           scaling=scaling, **kwargs)
         if attn_type == "a_shape":
             out = a_shape_kernel(query, key, value, {"attn_forward_config": attn_kwargs})
+        elif attn_type == "tri_shape":
+            out = tri_shape_kernel(query, key, value, {"attn_forward_config": attn_kwargs})
         else:
             cfg = attn_kwargs
             if attn_type == "dense":

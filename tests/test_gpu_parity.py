@@ -229,6 +229,43 @@ def test_streaming_attention_matches_oracle(dev, n, n_init, n_local):
     _close(out, ref[:, :, :n], (n, n_init, n_local))
 
 
+@pytest.mark.parametrize("n,n_last,n_init,n_local", [(1500, 100, 64, 256), (2048, 300, 128, 512), (700, 100, 128, 4096)])
+def test_tri_shape_matches_oracle(dev, n, n_last, n_init, n_local):
+    """A-shape rows (on the sequence cut before the last rows) + dense last rows
+    (ops/streaming_kernel.py:820-833 of the reference)."""
+    from minference_b200.ops.streaming_kernel import tri_shape_kernel
+    from minference_b200.synthetic import make_qkv
+    from oracle import reference_math as R
+
+    q, k, v = make_qkv(n, 4, 2, seed=21, dtype=torch.bfloat16)
+    out = tri_shape_kernel(q.to(dev), k.to(dev), v.to(dev),
+                           {"attn_forward_config": {"n_init": n_init, "n_local": n_local, "n_last": n_last}}).float().cpu()
+    cut = n - n_last
+    ref1 = R.streaming_attention_oracle(q[:, :, :cut], k[:, :, :cut], v[:, :, :cut], n_init, n_local)[:, :, :cut]
+    ref2 = torch.nn.functional.scaled_dot_product_attention(
+        q.float(), k.float().repeat_interleave(2, 1), v.float().repeat_interleave(2, 1), is_causal=True)[:, :, cut:]
+    d = (out - torch.cat([ref1, ref2], 2)).abs()
+    assert out.shape == (1, 4, n, 128) and d.max().item() < 2e-2 and d.mean().item() < 2e-3
+
+
+@pytest.mark.parametrize("kind", ["dilated1", "dilated2"])
+def test_dilated_index_sets_match_oracle(dev, kind):
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import dilated_sparse_attention
+    from minference_b200.synthetic import make_qkv
+    from oracle import reference_math as R
+
+    n = 2500
+    q, k, v = make_qkv(n, 2, 1, seed=22, dtype=torch.bfloat16)
+    out = dilated_sparse_attention(q.to(dev), k.to(dev), v.to(dev), kind).float().cpu()
+    pos = torch.arange(n)
+    pos = pos[-8192::2] if kind == "dilated1" else torch.cat([pos[-2048:], pos[-6144:-2048:2]], 0)
+    v_idx = torch.arange(min(1024, n))[None, None, :].expand(1, 2, -1)
+    s_idx = ((n - 1) - pos)[None, None, :].expand(1, 2, -1)
+    ref, _ = R.vertical_slash_attention_oracle(q, k, v, v_idx, s_idx)
+    d = (out - ref[:, :, :n]).abs()
+    assert d.max().item() < 2e-2 and d.mean().item() < 2e-3
+
+
 @pytest.mark.parametrize("n,top_k", [(1000, 5), (4096, 16), (1024, 100)])
 def test_block_sparse_matches_oracle(dev, n, top_k):
     from minference_b200.ops.block_sparse_flash_attention import _build_block_index, block_sparse_attention
