@@ -107,8 +107,10 @@ def count_tiles_window(plan, batch: int, heads: int, q_pos0: int, n_q: int, cap_
     return int(out.item())
 
 
-def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None):
-    """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``."""
+def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None,
+                     head_mode=None, head_param=None):
+    """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``.
+    ``head_mode`` / ``head_param`` select per head between the plan and the A-shape mask."""
     B, H, n_q, D = q.shape
     n_kv = k.shape[2]
     dev = q.device
@@ -119,13 +121,16 @@ def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx
             _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse),
             _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
             B, H, k.shape[1], n_ctx, n_q, q_pos0, n_kv, kv_pos0, D, float(sm_scale or D ** -0.5),
-            None, None, _cabi.ptr(plan), _cabi.ptr(v_idx), v_idx.shape[2], cap_s,
-            _cabi.ptr(status), _cabi.stream_ptr(dev)))
+            _cabi.ptr(head_mode), _cabi.ptr(head_param), _cabi.ptr(plan), _cabi.ptr(v_idx),
+            v_idx.shape[2] if v_idx is not None else 0, cap_s, _cabi.ptr(status), _cabi.stream_ptr(dev)))
     return out, lse
 
 
-def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size: int, slash_size: int, group=None):
-    """Global index lists from sharded K: ``(v_idx, s_idx, nnz_v, nnz_s)``, identical on all ranks."""
+def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_size, group=None,
+                                 cap_v: int | None = None, cap_s: int | None = None):
+    """Global index lists from sharded K: ``(v_idx, s_idx, nnz_v, nnz_s)``, identical on all ranks.
+    The budgets are ints (every head) or int32 tensors ``[H]`` with -1 for heads that are not
+    vertical-slash (their lists are left unset and ``nnz`` is -1); tensors need ``cap_v`` / ``cap_s``."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     B, H, n_loc, D = q_loc.shape
     Hkv = k_loc.shape[1]
@@ -157,9 +162,13 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size: int, s
     scores = torch.zeros((2, B, H, n_ctx), dtype=torch.float32, device=dev)
     run(2, all_stats, lambda i: 0, all_stats.shape[2], scores[0], scores[1])
     dist.all_reduce(scores, group=group)
-    cap_v, cap_s = min(n_ctx, max(vertical_size, 30)), min(n_ctx, max(slash_size, 50))
-    vs = torch.full((B * H,), vertical_size, dtype=torch.int32, device=dev)
-    ss = torch.full((B * H,), slash_size, dtype=torch.int32, device=dev)
+    if torch.is_tensor(vertical_size):
+        vs = vertical_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()
+        ss = slash_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()
+    else:
+        cap_v, cap_s = min(n_ctx, max(vertical_size, 30)), min(n_ctx, max(slash_size, 50))
+        vs = torch.full((B * H,), vertical_size, dtype=torch.int32, device=dev)
+        ss = torch.full((B * H,), slash_size, dtype=torch.int32, device=dev)
     v_idx = torch.empty((B, H, cap_v), dtype=torch.int32, device=dev)
     s_idx = torch.empty((B, H, cap_s), dtype=torch.int32, device=dev)
     nnz_v = torch.empty((B * H,), dtype=torch.int32, device=dev)
@@ -258,4 +267,36 @@ def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size
                              for (plan, _), qc in zip(plans, owned_chunks(rank, world)))
     for plan, status in plans:
         _cabi.raise_on_status(status, "ring_vertical_slash_attention")
+    return out
+
+
+def ring_prefill_attention(q_loc, k_loc, v_loc, n_ctx: int, pattern, group=None):
+    """Sequence-sharded attention of one layer with a per-head pattern table
+    (``modules.minference_forward.LayerPattern``): vertical-slash heads use the distributed
+    estimator and windowed plans, A-shape heads need no index; both run in the same launches.
+    Block-sparse heads are not sequence-sharded (their planner pools the whole K)."""
+    if pattern.any_bs:
+        raise _cabi.MInferB200Error("block-sparse heads are not supported under sequence sharding")
+    _cabi.require_cuda(q_loc, k_loc, v_loc)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    c = chunk_size(n_ctx, world)
+    dev = q_loc.device
+    plans, v_idx, cap_s = [], None, 1
+    if pattern.any_vs:
+        v_idx, s_idx, nnz_v, nnz_s = ring_vertical_slash_estimate(
+            q_loc, k_loc, n_ctx, pattern.vertical_size, pattern.slash_size, group, cap_v=pattern.cap_v, cap_s=pattern.cap_s)
+        cap_s = s_idx.shape[2]
+        for qc in owned_chunks(rank, world):
+            plans.append(build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx, qc * c, c))
+    else:
+        plans = [(None, _cabi.new_status(dev)) for _ in owned_chunks(rank, world)]
+
+    def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
+        plan, status = plans[qi]
+        return attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, cap_s, status,
+                                head_mode=pattern.head_mode, head_param=pattern.head_param)
+
+    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
+    for _, status in plans:
+        _cabi.raise_on_status(status, "ring_prefill_attention")
     return out

@@ -379,3 +379,41 @@ def test_full_size_properties_131072(dev):
         ref = R.masked_attention_rows(qc[m * 64:m * 64 + 64], kc, vc, mask, m * 64)
         d = (out[0, 0, m * 64:m * 64 + 64].float().cpu() - ref).abs()
         assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (m, d.max().item())
+
+
+def test_full_size_mixed_patterns_262144(dev):
+    """BASELINE mixed-pattern layer shape (28 query / 4 KV heads, 262144 tokens): V = 1 must give 1
+    for every head pattern (each row's weights sum to one), and sampled row blocks of an A-shape
+    head and a block-sparse head match the masked-dense oracle."""
+    from minference_b200.modules.minference_forward import minference_prefill_forward
+    from minference_b200.ops.block_sparse_flash_attention import _build_block_index
+    from minference_b200.synthetic import make_qkv
+    from oracle import reference_math as R
+
+    n, hq, hkv = 262144, 28, 4
+    q, k, v = make_qkv(n, hq, hkv, seed=1, dtype=torch.bfloat16, device=dev)
+    kinds = ["stream_llm", "vertical_and_slash", "block_sparse"]
+    table = {str(h): ([kinds[h % 3], 128, 4096, 1.0] if h % 3 == 0 else
+                      [kinds[h % 3], 1000, 6096, 1.0] if h % 3 == 1 else [kinds[h % 3], 100, 0, 1.0]) for h in range(hq)}
+    kw = {"attn_forward_config": {"best_pattern": [table]}, "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
+    ones = minference_prefill_forward(q, k, torch.ones_like(v), kw)
+    assert (ones.float() - 1).abs().max().item() < 1e-2
+    out = minference_prefill_forward(q, k, v, kw)
+    rows = n // 64
+    rep = hq // hkv
+    # A-shape head 0
+    kc, vc = k[0, 0].float().cpu(), v[0, 0].float().cpu()
+    for m in (0, 63, 64, 65, rows // 3, rows - 1):
+        mask = R.a_shape_mask_rows(n, 128, 4096, m * 64, m * 64 + 64)
+        ref = R.masked_attention_rows(q[0, 0, m * 64:m * 64 + 64].float().cpu(), kc, vc, mask, m * 64)
+        d = (out[0, 0, m * 64:m * 64 + 64].float().cpu() - ref).abs()
+        assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, ("a_shape", m, d.max().item())
+    # block-sparse head 2 (index taken from the GPU planner: ties in the pooled bf16 scores are unpinned)
+    h = 2
+    bidx = _build_block_index(q[:, h:h + 1], k[:, h // rep:h // rep + 1], 100)[0, 0].cpu().numpy()
+    kc, vc = k[0, h // rep].float().cpu(), v[0, h // rep].float().cpu()
+    for m in (0, 5, 150, rows // 2, rows - 1):
+        mask = R.block_sparse_mask_rows(bidx, n, [m])
+        ref = R.masked_attention_rows(q[0, h, m * 64:m * 64 + 64].float().cpu(), kc, vc, mask, m * 64)
+        d = (out[0, h, m * 64:m * 64 + 64].float().cpu() - ref).abs()
+        assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, ("block_sparse", m, d.max().item())

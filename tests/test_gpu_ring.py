@@ -110,6 +110,49 @@ def test_sharded_estimator_stages_match_whole_sequence(dev):
         assert len(set(s_idx[0, h].tolist()) & set(s_ref[0, h].tolist())) >= 594
 
 
+@pytest.mark.parametrize("world,n,n_init,n_local", [(2, 4096, 128, 512), (4, 8192, 64, 1500)])
+def test_windowed_kernel_pairs_merge_mixed_a_shape_and_vertical_slash(dev, world, n, n_init, n_local):
+    """Heads 0 and 2 vertical-slash, heads 1 and 3 A-shape, in the same windowed launches."""
+    from minference_b200 import _cabi
+    from minference_b200.dist import ring
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import local_vs_indices, make_qkv
+    from oracle import reference_math as R
+
+    hq, hkv = 4, 2
+    q, k, v = make_qkv(n, hq, hkv, seed=9, dtype=torch.bfloat16)
+    vi, si = local_vs_indices(n, hq, 64, 300, seed=5)
+    vs, ss = R.presort_indices(vi, si, 1, hq)
+    dq, dk, dv, dvs, dss = (t.to(dev) for t in (q, k, v, vs.contiguous(), ss.contiguous()))
+    mode = torch.tensor([_cabi.MODE_PLAN, _cabi.MODE_ASHAPE] * 2, dtype=torch.int32, device=dev)
+    param = torch.tensor([[0, 0], [n_init, n_local]] * 2, dtype=torch.int32, device=dev)
+    full = sparse_attention_forward(dq, dk, dv, build_vertical_slash_plan(dvs, dss, n), head_mode=mode, head_param=param)
+    c = ring.chunk_size(n, world)
+    parts = []
+    for r in range(world):
+        outs = []
+        for qc in ring.owned_chunks(r, world):
+            plan, status = ring.build_plan_window(dvs, dss, None, None, n, qc * c, c)
+            acc_o = torch.zeros(1, hq, c, 128, device=dev)
+            acc_l = torch.full((1, hq, c), float("-inf"), device=dev)
+            for kc in range(2 * world):
+                if not ring.pair_is_visible(qc, kc):
+                    continue
+                o, lse = ring.attention_window(dq[:, :, qc * c:(qc + 1) * c], dk[:, :, kc * c:(kc + 1) * c],
+                                               dv[:, :, kc * c:(kc + 1) * c], n, qc * c, kc * c, plan, dvs,
+                                               dss.shape[2], status, head_mode=mode, head_param=param)
+                ring.merge_partial(acc_o, acc_l, o, lse)
+            assert status.tolist()[:2] == [0, 0]
+            outs.append(acc_o)
+        parts.append(torch.cat(outs, dim=2))
+    merged = ring.zigzag_merge(parts, world)
+    assert (merged - full.float()).abs().max().item() < 1.5e-2
+    ref = R.streaming_attention_oracle(q[:, 1:2].float(), k[:, 0:1].float(), v[:, 0:1].float(), n_init, n_local)
+    d = (merged[:, 1:2].cpu() - ref[:, :, :n]).abs()
+    assert d.max().item() < 2e-2 and d.mean().item() < 2e-3
+
+
 def test_real_ring_on_two_gpus():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
