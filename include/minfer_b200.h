@@ -107,6 +107,22 @@ int minf_block_sparse_build_plan(
     void* scratch, int32_t* status, void* stream);
 
 /*
+ * The same planner in two steps for a sequence-sharded caller (no counterpart in the reference,
+ * which has no sequence parallelism).  minf_block_sparse_pool: mean of each block of 64 rows of
+ * `x` [batch, heads, n_rows, 128] -> `pooled` bf16 [batch, heads, ceil(n_rows/64), 128] (a ragged
+ * last block is divided by 64 like the reference's zero padding).  The caller gathers the pooled
+ * keys of the whole sequence in order.  minf_block_sparse_select_window: top-k key blocks for the
+ * query blocks of rows [q_pos0, q_pos0 + n_q) (q_pos0 a multiple of 64) from `q_pooled`
+ * [batch, hq, ceil(n_q/64), 128] and `k_pooled` [batch, hkv, ceil(context_size/64), 128], written
+ * into a window plan (minf_plan_bytes_window) for the heads `head_select` marks.
+ */
+int minf_block_sparse_pool(
+    const void* x, const int64_t strides[3], int batch, int heads, int n_rows, void* pooled, void* stream);
+int minf_block_sparse_select_window(
+    const void* q_pooled, const void* k_pooled, int batch, int hq, int hkv, int context_size,
+    int q_pos0, int n_q, int top_k, const int32_t* head_select, int cap_v, int cap_s, void* plan, void* stream);
+
+/*
  * Online vertical/slash index estimation for all heads in one call.  Replaces the torch
  * ops of vertical_and_slash_kernel (modules/minference_forward.py:599-614) and
  * sum_all_diagonal_matrix (:110-116): last-64-query x K^T logits, causal mask of the last

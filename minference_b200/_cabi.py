@@ -35,6 +35,8 @@ SIGNATURES = {
     "minf_block_sparse_scratch_bytes": (c_size_t, [c_int] * 4),
     "minf_block_sparse_build_plan": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 6 + [c_void_p] +
                                      [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "minf_block_sparse_pool": (c_int, [c_void_p, _I64x3, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "minf_block_sparse_select_window": (c_int, [c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "minf_vs_estimate_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_estimate": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
                          [c_int, c_int] + [c_void_p] * 6 + [c_void_p, c_void_p, c_void_p]),

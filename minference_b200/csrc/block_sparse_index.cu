@@ -63,6 +63,8 @@ struct BsSelectArgs {
     int32_t* block_index;    // optional [batch, hq, rows_pad, top_k]
     unsigned char* plan;     // optional
     PlanLayout layout;
+    int m_base;              // query block of blockIdx.x = 0 (sequence-sharded callers plan a window of query blocks)
+    int rows_q;              // query blocks held by qpool per head (rows_pad for a whole sequence)
 };
 
 // order-preserving map of a float to uint32
@@ -80,7 +82,8 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     __shared__ int sh_base, sh_ties;
     __shared__ unsigned char take_flag[256];
 
-    const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int m_loc = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int m = a.m_base + m_loc;           // position of the query block in the sequence
     if (a.head_select && a.head_select[h] == 0) return;
     const int hk = h / (a.hq / a.hkv);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     const int n_blocks = m + 1;               // causal key blocks 0..m
     const int k = min(a.top_k, n_blocks);     // blocks the attention kernel consumes (:81)
 
-    if (threadIdx.x < 128) qv[threadIdx.x] = __bfloat162float(a.qpool[(bh * a.rows_pad + m) * 128 + threadIdx.x]);
+    if (threadIdx.x < 128) qv[threadIdx.x] = __bfloat162float(a.qpool[(bh * a.rows_q + m_loc) * 128 + threadIdx.x]);
     __syncthreads();
     const __nv_bfloat16* kp = a.kpool + ((size_t)b * a.hkv + hk) * a.rows_pad * 128;
     for (int n = warp; n < n_blocks; n += 8) {
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     int32_t* bi = a.block_index ? a.block_index + (bh * a.rows_pad + m) * a.top_k : nullptr;
     int2* rng = nullptr;
     if (a.plan && m < a.rows)
-        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_offset(a.layout, m);
+        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_offset(a.layout, m_loc);
     if (threadIdx.x == 0) { sh_base = 0; sh_ties = 0; }
     __syncthreads();
     int nrng = 0;          // maintained by thread 0 only
@@ -181,10 +184,10 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     }
     if (threadIdx.x == 0 && rng) {
         if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
-        reinterpret_cast<int32_t*>(a.plan + bh * a.layout.head_bytes)[m] = nrng;
+        reinterpret_cast<int32_t*>(a.plan + bh * a.layout.head_bytes)[m_loc] = nrng;
     }
     if (a.plan && m < a.rows) {
-        uint32_t* wb = reinterpret_cast<uint32_t*>(a.plan + bh * a.layout.head_bytes + a.layout.bits_off) + (size_t)m * a.layout.words_v;
+        uint32_t* wb = reinterpret_cast<uint32_t*>(a.plan + bh * a.layout.head_bytes + a.layout.bits_off) + (size_t)m_loc * a.layout.words_v;
         for (int w = threadIdx.x; w < a.layout.words_v; w += blockDim.x) wb[w] = 0u;
     }
     // tail of the reference-format row: the reference holds arbitrary masked block ids there
@@ -242,9 +245,55 @@ extern "C" int minf_block_sparse_build_plan(
     s.block_index = block_index_out;
     s.plan = static_cast<unsigned char*>(plan);
     s.layout = make_plan_layout(context_size, cap_v, cap_s);
+    s.m_base = 0; s.rows_q = rows_pad;
     const size_t smem = (size_t)rows_pad * sizeof(uint32_t);
     MINF_CUDA_OK(cudaFuncSetAttribute(bs_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     bs_select_kernel<<<dim3(rows_pad, hq, batch), 256, smem, st>>>(s);
+    MINF_LAUNCH_OK("bs_select_kernel");
+    return MINF_OK;
+}
+
+extern "C" int minf_block_sparse_pool(
+    const void* x, const int64_t strides[3], int batch, int heads, int n_rows, void* pooled, void* stream) {
+    if (!x || !strides || !pooled) return fail(MINF_E_ARG, "null pointer argument");
+    if (batch < 1 || heads < 1 || n_rows < 1) return fail(MINF_E_ARG, "bad sizes");
+    for (int i = 0; i < 3; ++i)
+        if (strides[i] % 4) return fail(MINF_E_ARG, "strides must be multiples of 4 elements");
+    PoolArgs p{};
+    p.q = static_cast<const __nv_bfloat16*>(x); p.k = nullptr;
+    p.q_sb = strides[0]; p.q_sh = strides[1]; p.q_sn = strides[2];
+    p.batch = batch; p.hq = heads; p.hkv = 0; p.n_ctx = n_rows; p.rows_pad = (n_rows + 63) / 64;
+    p.qpool = static_cast<__nv_bfloat16*>(pooled); p.kpool = nullptr;
+    const long long warps = (long long)batch * heads * p.rows_pad;
+    bs_pool_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    MINF_LAUNCH_OK("bs_pool_kernel");
+    return MINF_OK;
+}
+
+extern "C" int minf_block_sparse_select_window(
+    const void* q_pooled, const void* k_pooled, int batch, int hq, int hkv, int context_size,
+    int q_pos0, int n_q, int top_k, const int32_t* head_select, int cap_v, int cap_s, void* plan, void* stream) {
+    if (!q_pooled || !k_pooled || !plan) return fail(MINF_E_ARG, "null pointer argument");
+    if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1 || top_k < 1 || batch > 65535 || hq > 65535)
+        return fail(MINF_E_ARG, "bad sizes");
+    if (q_pos0 < 0 || (q_pos0 % 64) || n_q < 1 || q_pos0 + n_q > context_size) return fail(MINF_E_ARG, "bad query window");
+    const int rows_k = (context_size + 63) / 64;
+    const int rows_loc = (n_q + 63) / 64;
+    const int k_eff = top_k < bs_rows_pad(context_size) ? top_k : bs_rows_pad(context_size);
+    if (cap_s < k_eff) return fail(MINF_E_ARG, "cap_s=%d is smaller than top_k=%d", cap_s, k_eff);
+    if ((size_t)rows_k * 4 > 160 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
+    BsSelectArgs s{};
+    s.qpool = static_cast<const __nv_bfloat16*>(q_pooled); s.kpool = static_cast<const __nv_bfloat16*>(k_pooled);
+    s.batch = batch; s.hq = hq; s.hkv = hkv; s.n_ctx = context_size;
+    s.rows = rows_k; s.rows_pad = rows_k; s.top_k = k_eff;
+    s.head_select = head_select;
+    s.block_index = nullptr;
+    s.plan = static_cast<unsigned char*>(plan);
+    s.layout = make_plan_layout_window(q_pos0 / 64, rows_loc, cap_v, cap_s);
+    s.m_base = q_pos0 / 64; s.rows_q = rows_loc;
+    const size_t smem = (size_t)rows_k * sizeof(uint32_t);
+    MINF_CUDA_OK(cudaFuncSetAttribute(bs_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bs_select_kernel<<<dim3(rows_loc, hq, batch), 256, smem, static_cast<cudaStream_t>(stream)>>>(s);
     MINF_LAUNCH_OK("bs_select_kernel");
     return MINF_OK;
 }

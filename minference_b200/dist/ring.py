@@ -108,7 +108,7 @@ def count_tiles_window(plan, batch: int, heads: int, q_pos0: int, n_q: int, cap_
 
 
 def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None,
-                     head_mode=None, head_param=None):
+                     head_mode=None, head_param=None, cap_v: int | None = None):
     """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``.
     ``head_mode`` / ``head_param`` select per head between the plan and the A-shape mask."""
     B, H, n_q, D = q.shape
@@ -122,7 +122,8 @@ def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx
             _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
             B, H, k.shape[1], n_ctx, n_q, q_pos0, n_kv, kv_pos0, D, float(sm_scale or D ** -0.5),
             _cabi.ptr(head_mode), _cabi.ptr(head_param), _cabi.ptr(plan), _cabi.ptr(v_idx),
-            v_idx.shape[2] if v_idx is not None else 0, cap_s, _cabi.ptr(status), _cabi.stream_ptr(dev)))
+            cap_v if cap_v is not None else (v_idx.shape[2] if v_idx is not None else 0), cap_s,
+            _cabi.ptr(status), _cabi.stream_ptr(dev)))
     return out, lse
 
 
@@ -270,31 +271,59 @@ def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size
     return out
 
 
-def ring_prefill_attention(q_loc, k_loc, v_loc, n_ctx: int, pattern, group=None):
+def _pooled_blocks(x):
+    """bf16 means of the 64-row blocks of ``x [B,H,n,128]`` -> ``[B,H,ceil(n/64),128]``."""
+    B, H, n, D = x.shape
+    x = x if x.stride(3) == 1 else x.contiguous()
+    out = torch.empty((B, H, (n + 63) // 64, D), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(_cabi.lib().minf_block_sparse_pool(_cabi.ptr(x), _cabi.strides3(x), B, H, n, _cabi.ptr(out),
+                                                       _cabi.stream_ptr(x.device)))
+    return out
+
+
+def ring_prefill_attention(q_loc, k_loc, v_loc, n_ctx: int, pattern, group=None, block_sparse_top_k: int = 100):
     """Sequence-sharded attention of one layer with a per-head pattern table
-    (``modules.minference_forward.LayerPattern``): vertical-slash heads use the distributed
-    estimator and windowed plans, A-shape heads need no index; both run in the same launches.
-    Block-sparse heads are not sequence-sharded (their planner pools the whole K)."""
-    if pattern.any_bs:
-        raise _cabi.MInferB200Error("block-sparse heads are not supported under sequence sharding")
+    (``modules.minference_forward.LayerPattern``).  Vertical-slash heads use the distributed
+    estimator and windowed plans; block-sparse heads pool their local Q and K, all-gather the
+    pooled keys (``n_ctx/64`` vectors per KV head) and select their blocks locally; A-shape heads
+    need no index.  All heads run in the same launches."""
     _cabi.require_cuda(q_loc, k_loc, v_loc)
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     c = chunk_size(n_ctx, world)
     dev = q_loc.device
-    plans, v_idx, cap_s = [], None, 1
+    B, H = q_loc.shape[0], q_loc.shape[1]
+    L = _cabi.lib()
+    chunks = owned_chunks(rank, world)
+    v_idx, cap_v, cap_s = None, (pattern.cap_v if pattern.any_vs else 0), pattern.cap_s
+    plans = []
     if pattern.any_vs:
         v_idx, s_idx, nnz_v, nnz_s = ring_vertical_slash_estimate(
             q_loc, k_loc, n_ctx, pattern.vertical_size, pattern.slash_size, group, cap_v=pattern.cap_v, cap_s=pattern.cap_s)
-        cap_s = s_idx.shape[2]
-        for qc in owned_chunks(rank, world):
+        for qc in chunks:
             plans.append(build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx, qc * c, c))
+    elif pattern.any_bs:
+        for qc in chunks:
+            plan = torch.empty(L.minf_plan_bytes_window(B, H, qc * c, c, cap_v, cap_s), dtype=torch.uint8, device=dev)
+            plans.append((plan, _cabi.new_status(dev)))
     else:
-        plans = [(None, _cabi.new_status(dev)) for _ in owned_chunks(rank, world)]
+        plans = [(None, _cabi.new_status(dev)) for _ in chunks]
+    if pattern.any_bs:
+        k_pool = _pooled_blocks(k_loc)                               # [B, Hkv, 2c/64, 128], this rank's two chunks
+        gathered = [torch.empty_like(k_pool) for _ in range(world)]
+        dist.all_gather(gathered, k_pool, group=group)
+        k_pool_all = zigzag_merge(gathered, world).contiguous()      # blocks of the whole sequence in order
+        for qi, qc in enumerate(chunks):
+            q_pool = _pooled_blocks(q_loc[:, :, qi * c:(qi + 1) * c])
+            with torch.cuda.device(dev):
+                _cabi.check(L.minf_block_sparse_select_window(
+                    _cabi.ptr(q_pool), _cabi.ptr(k_pool_all), B, H, k_loc.shape[1], n_ctx, qc * c, c, int(block_sparse_top_k),
+                    _cabi.ptr(pattern.block_select), cap_v, cap_s, _cabi.ptr(plans[qi][0]), _cabi.stream_ptr(dev)))
 
     def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
         plan, status = plans[qi]
         return attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, cap_s, status,
-                                head_mode=pattern.head_mode, head_param=pattern.head_param)
+                                head_mode=pattern.head_mode, head_param=pattern.head_param, cap_v=cap_v)
 
     out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
     for _, status in plans:

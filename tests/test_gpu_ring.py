@@ -153,6 +153,39 @@ def test_windowed_kernel_pairs_merge_mixed_a_shape_and_vertical_slash(dev, world
     assert d.max().item() < 2e-2 and d.mean().item() < 2e-3
 
 
+@pytest.mark.parametrize("world,n,top_k", [(2, 4096, 6), (4, 8192, 20)])
+def test_windowed_block_sparse_planner_matches_whole_sequence(dev, world, n, top_k):
+    """Pooled keys of the whole sequence + per-chunk block selection (the sequence-sharded planner)
+    give the same attention as the whole-sequence block-sparse operator."""
+    from minference_b200 import _cabi
+    from minference_b200.dist import ring
+    from minference_b200.ops.block_sparse_flash_attention import block_sparse_attention
+    from minference_b200.synthetic import make_qkv
+
+    hq, hkv = 4, 2
+    q, k, v = (t.to(dev) for t in make_qkv(n, hq, hkv, seed=10, dtype=torch.bfloat16))
+    full = block_sparse_attention(q, k, v, top_k).float()
+    L = _cabi.lib()
+    c = ring.chunk_size(n, world)
+    k_pool_all = torch.cat([ring._pooled_blocks(k[:, :, ch * c:(ch + 1) * c]) for ch in range(2 * world)], dim=2).contiguous()
+    merged = torch.zeros(1, hq, n, 128, device=dev)
+    for qc in range(2 * world):
+        plan = torch.empty(L.minf_plan_bytes_window(1, hq, qc * c, c, 0, top_k), dtype=torch.uint8, device=dev)
+        status = _cabi.new_status(dev)
+        q_pool = ring._pooled_blocks(q[:, :, qc * c:(qc + 1) * c])
+        _cabi.check(L.minf_block_sparse_select_window(_cabi.ptr(q_pool), _cabi.ptr(k_pool_all), 1, hq, hkv, n, qc * c, c, top_k,
+                                                      None, 0, top_k, _cabi.ptr(plan), _cabi.stream_ptr(dev)))
+        acc_o = torch.zeros(1, hq, c, 128, device=dev)
+        acc_l = torch.full((1, hq, c), float("-inf"), device=dev)
+        for kc in range(qc + 1):
+            o, lse = ring.attention_window(q[:, :, qc * c:(qc + 1) * c], k[:, :, kc * c:(kc + 1) * c], v[:, :, kc * c:(kc + 1) * c],
+                                           n, qc * c, kc * c, plan, None, top_k, status, cap_v=0)
+            ring.merge_partial(acc_o, acc_l, o, lse)
+        assert status.tolist()[:2] == [0, 0]
+        merged[:, :, qc * c:(qc + 1) * c] = acc_o
+    assert (merged - full).abs().max().item() < 1.5e-2
+
+
 def test_real_ring_on_two_gpus():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
