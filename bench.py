@@ -515,8 +515,10 @@ TTFT_WORKLOADS = {
     "llama3_8b_512k_ttft": (524288, 32),
     "llama3_8b_128k_ttft": (131072, 32),
     "llama3_8b_32k_ttft_4layers": (32768, 4),
-    # vertical-slash on every head; with N > 1 ranks the prompt is sequence-sharded (zigzag ring)
+    "llama3_8b_1m_ttft": (1048576, 32),
+    # vertical-slash on every head (BASELINE configs[4] extended to the whole model)
     "llama3_8b_1m_ttft_vs": (1048576, 32),
+    "llama3_8b_256k_ttft_4layers": (262144, 4),
     "llama3_8b_256k_ttft_vs_4layers": (262144, 4),
 }
 
@@ -546,8 +548,6 @@ def run_ttft_arm(args, wl):
     shape = LlamaShape(layers=layers)
     model = LlamaPrefill(shape, dev, seed=0)            # same seed: identical weights on every rank
     vs_only = wl.endswith("_vs") or "_vs_" in wl
-    if world > 1 and not vs_only:
-        raise SystemExit("only the vertical-slash TTFT workloads are sequence-sharded")
     tables = seeded_pattern_tables(shape, seed=0, kinds=("vertical_and_slash",) if vs_only else
                                    ("stream_llm", "vertical_and_slash", "block_sparse"))
     cfg = {"starting_layer": 0, "best_pattern": tables}
@@ -555,7 +555,12 @@ def run_ttft_arm(args, wl):
     positions = zigzag_positions(n, rank, world, dev) if world > 1 else None
     ids_host = (ids_all[positions.cpu()] if world > 1 else ids_all).pin_memory()
     logits_host = torch.empty(shape.vocab, dtype=torch.float32).pin_memory()
-    attention = (lambda q, k, v, li: ring.ring_vertical_slash_attention(q, k, v, n, 1000, 6096)) if world > 1 else None
+    attention = None
+    if world > 1:       # with N > 1 ranks the prompt is sequence-sharded (zigzag chunks) and attention is the ring
+        from minference_b200.modules.minference_forward import LayerPattern
+
+        patterns = [LayerPattern(t, shape.q_heads, n, None, dev) for t in tables]
+        attention = lambda q, k, v, li: ring.ring_prefill_attention(q, k, v, n, patterns[li])
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     def step():
