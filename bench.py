@@ -516,7 +516,7 @@ TTFT_WORKLOADS = {
     "llama3_8b_128k_ttft": (131072, 32),
     "llama3_8b_32k_ttft_4layers": (32768, 4),
     "llama3_8b_1m_ttft": (1048576, 32),
-    # vertical-slash on every head (BASELINE configs[4] extended to the whole model)
+    # vertical-slash on every head (the 1M-token ring configuration extended to the whole model)
     "llama3_8b_1m_ttft_vs": (1048576, 32),
     "llama3_8b_256k_ttft_4layers": (262144, 4),
     "llama3_8b_256k_ttft_vs_4layers": (262144, 4),

@@ -382,7 +382,7 @@ def test_full_size_properties_131072(dev):
 
 
 def test_full_size_mixed_patterns_262144(dev):
-    """BASELINE mixed-pattern layer shape (28 query / 4 KV heads, 262144 tokens): V = 1 must give 1
+    """Mixed-pattern layer of the Qwen2.5-7B head geometry (28 query / 4 KV heads, 262144 tokens): V = 1 must give 1
     for every head pattern (each row's weights sum to one), and sampled row blocks of an A-shape
     head and a block-sparse head match the masked-dense oracle."""
     from minference_b200.modules.minference_forward import minference_prefill_forward
