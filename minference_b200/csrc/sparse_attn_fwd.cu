@@ -9,7 +9,8 @@
 //                   vertical columns (cp.async) -- with a 128-bit key mask per row block.
 //                   K and V travel through separate rings so a K stage is recycled as soon as
 //                   both QK^T products have read it.
-//   warp 1          issues every tcgen05.mma (lane 0) and owns the TMEM allocation
+//   warp 1          issues every tcgen05.mma and tcgen05.commit (the whole warp follows the control
+//                   flow, one lane elected per instruction) and owns the TMEM allocation
 //   warps 2-3       spare (they keep the roles aligned to warpgroups of four; setmaxnreg hands
 //                   their registers to the softmax warps)
 //   warps 4-7/8-11  softmax of slot 0 / slot 1, one thread per query row, the whole 128-key row
@@ -17,7 +18,9 @@
 // TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written back
 // over the first half of S and feeds the PV product straight from TMEM, so it never touches
 // shared memory.  The two slots alternate: while one slot's softmax runs, the tensor pipe
-// executes the other slot's PV and next QK^T.
+// executes the other slot's PV and next QK^T.  CTAs are ordered one KV head at a time (its query
+// heads and all their 256-row items, most work first) so that the CTAs in flight share K/V in L2.
+// status[2..3] (one uint64) counts the 64x64 tile equivalents sent to the tensor pipe.
 //
 // Positions are global token positions throughout; `q_pos0` / `kv_pos0` say where the local Q
 // and K/V tensors sit in the sequence, so the same kernel serves a whole sequence on one GPU
