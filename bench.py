@@ -65,14 +65,17 @@ def mixed_pattern_table(hq: int, vsize: int, ssize: int, seed: int = 3):
 
 
 def a_shape_tiles(n: int, n_init: int, n_local: int) -> int:
-    """64x64 tiles of one A-shape head: window tiles of every row block plus the sink tiles of the
-    row blocks that reach past the window (the algorithmic count; masked-out sink tiles excluded)."""
+    """64x64 tiles the reference's two stages compute for one A-shape head: the tiles that meet the
+    window of a row block, plus the sink tiles that hold a key at distance >= n_local from one of
+    its rows (sink tiles masked out entirely are not counted)."""
     total = 0
     for m in range((n + 63) // 64):
         lo = max(64 * m - n_local + 1, 0) // 64
         total += m - lo + 1
-        if 64 * m + 63 >= n_local:
-            total += (n_init + 63) // 64
+        if n > n_local:
+            for t in range((n_init + 63) // 64):
+                if 64 * (m - t) + 63 >= n_local:
+                    total += 1
     return total
 
 

@@ -81,3 +81,77 @@ def test_patched_llama_matches_dense_when_budgets_cover_everything(tmp_path):
     with torch.no_grad():
         out2 = model(ids, use_cache=False).logits.float()
     assert torch.isfinite(out2).all()
+
+
+def test_search_and_record_appends_one_layer_per_call(tmp_path, monkeypatch):
+    """Bookkeeping of the offline search (the JSON file grows by one layer per call, a finished
+    file is refused like modules/minference_forward.py:646-650 of the reference); the scoring
+    itself needs the GPU and is tested there."""
+    import json
+
+    from minference_b200.modules import pattern_search
+
+    calls = []
+
+    def fake_search(q, k, v, **kw):
+        calls.append(1)
+        return {0: ("vertical_and_slash", 100, 750, 0.9), 1: ("vertical_and_slash", 1000, 6096, 0.8)}
+
+    monkeypatch.setattr(pattern_search, "search_layer_patterns", fake_search)
+    path = str(tmp_path / "table.json")
+    for layer in range(2):
+        got = pattern_search.search_and_record(None, None, None, layer, 2, path)
+        assert got == {"0": ["vertical_and_slash", 100, 750, 0.9], "1": ["vertical_and_slash", 1000, 6096, 0.8]}
+    assert len(json.load(open(path))) == 2 and len(calls) == 2
+    with pytest.raises(RuntimeError):
+        pattern_search.search_and_record(None, None, None, 0, 2, path)
+    # a layer that is already in an unfinished file is not searched again
+    path2 = str(tmp_path / "partial.json")
+    pattern_search.search_and_record(None, None, None, 0, 3, path2)
+    pattern_search.search_and_record(None, None, None, 0, 3, path2)
+    assert len(json.load(open(path2))) == 1 and len(calls) == 3
+
+
+def test_configuration_accepts_search_and_tri_shape(tmp_path):
+    from minference_b200 import MInferenceConfig
+
+    cfg = MInferenceConfig(attn_type="minference", is_search=True, config_path=str(tmp_path / "t.json"))
+    assert cfg.attn_kwargs["is_search"] is True and cfg.attn_kwargs["config_path"].endswith("t.json")
+    with pytest.raises(ValueError):
+        MInferenceConfig(attn_type="minference", is_search=True, model_name="unregistered-model")
+    assert MInferenceConfig(attn_type="tri_shape").attn_type == "tri_shape"
+    assert "tri_shape" in MInferenceConfig.get_available_attn_types()
+
+
+def test_bench_tile_formulas_match_the_oracle_masks():
+    import numpy as np
+
+    import bench
+    from oracle import reference_math as R
+
+    for n, n_init, n_local in ((2048, 128, 512), (1500, 100, 300), (600, 128, 4096)):
+        tiles = 0
+        i = np.arange(n)[:, None]
+        j = np.arange(n)[None, :]
+        window = ((i - j) >= 0) & ((i - j) < n_local)                       # stage 1 of the reference
+        sinks = (j < n_init) & ((i - j) >= n_local) if n > n_local else np.zeros((n, n), bool)    # stage 2
+        pad = (-n) % 64
+        for mask in (window, sinks):
+            mp = np.pad(mask, ((0, pad), (0, pad)))
+            tiles += int(np.any(mp.reshape((n + pad) // 64, 64, (n + pad) // 64, 64), axis=(1, 3)).sum())
+        assert bench.a_shape_tiles(n, n_init, n_local) == tiles, (n, n_init, n_local)
+        assert np.array_equal(window | sinks, R.a_shape_mask_rows(n, n_init, n_local, 0, n))
+    t1, k1 = bench.mixed_pattern_table(28, 1000, 6096)
+    t2, k2 = bench.mixed_pattern_table(28, 1000, 6096)
+    assert t1 == t2 and set(k1) == {0, 1, 2}
+
+
+def test_zigzag_positions_cover_the_sequence():
+    import torch
+
+    from minference_b200.prefill_runner import zigzag_positions
+
+    n, world = 256 * 8, 4
+    allpos = torch.cat([zigzag_positions(n, r, world) for r in range(world)])
+    assert sorted(allpos.tolist()) == list(range(n))
+    assert zigzag_positions(n, 0, world)[-1].item() == n - 1      # the last token is rank 0's last token
