@@ -199,6 +199,42 @@ def test_vertical_slash_attention_matches_oracle(dev, n, hq, hkv, nv, ns, kind):
     _close(out, ref[:, :, :n], (n, kind))
 
 
+@pytest.mark.parametrize("n,hq,hkv,nv,ns,kind", [(2048, 4, 2, 120, 260, "uniform"), (1000, 2, 2, 64, 300, "local"),
+                                                 (4096, 4, 1, 1000, 3000, "estimated")])
+def test_attention_matches_reference_triton_kernel_on_gpu(dev, n, hq, hkv, nv, ns, kind):
+    """The reference's own attention kernel (compiled ahead of time from the reference tree by
+    oracle/build_ref.py --triton) and the product kernel on the same inputs and index tensors."""
+    from oracle import ref_triton
+
+    if not ref_triton.available():
+        pytest.skip("the reference's Triton kernel was not compiled (oracle/_ref/ref_triton_vs_fwd.cubin)")
+    from minference_b200.cuda import convert_vertical_slash_indexes
+    from minference_b200.modules.minference_forward import vertical_slash_estimate
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import vertical_slash_sparse_attention
+    from minference_b200.synthetic import local_vs_indices, make_qkv
+    from oracle import reference_math as R
+    from tests.golden.make_golden import index_case
+
+    q, k, v = (t.to(dev) for t in make_qkv(n, hq, hkv, seed=31, dtype=torch.bfloat16))
+    if kind == "local":
+        vi, si = local_vs_indices(n, hq, nv, ns, seed=6)
+    elif kind == "uniform":
+        a, b = index_case(5, n, hq, nv, ns, "uniform")
+        b[..., -1] = 0
+        vi, si = torch.from_numpy(a), torch.from_numpy(b)
+    else:
+        vi, si, _, _ = vertical_slash_estimate(q, k, nv, ns)
+    vs, ss = R.presort_indices(vi.cpu(), si.cpu(), 1, hq)
+    vs, ss = vs.contiguous().to(dev), ss.contiguous().to(dev)
+    bc, bo, cc, ci = convert_vertical_slash_indexes(torch.tensor([n], dtype=torch.int32, device=dev), vs, ss, n)
+    ref = ref_triton.reference_vertical_slash_attention(ref_triton.ReferenceTritonKernel(), q, k, v, bc, bo, cc, ci).float()
+    out = vertical_slash_sparse_attention(q, k, v, vs, ss).float()
+    torch.cuda.synchronize()
+    d = (out - ref).abs()
+    assert torch.isfinite(ref).all() and ref.abs().max().item() > 0.1
+    assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
+
+
 def test_attention_accepts_strided_layout_and_repeated_kv(dev):
     """[B,N,H,D] memory viewed as [B,H,N,D] (the layout HF projections produce) and K/V already
     repeated to the query head count, as the reference's caller passes them."""
