@@ -1,9 +1,11 @@
 """TEST INFRASTRUCTURE ONLY -- runs the reference's own Triton attention kernel on the GPU.
 
-``oracle/build_ref.py --triton`` compiles ``_triton_mixed_sparse_attn_fwd_kernel`` of the reference
-(ops/pit_sparse_flash_attention_v2.py:48-153) ahead of time into ``oracle/_ref``; this module loads
-that binary through the CUDA driver API and launches it the way the reference's launcher does
-(:156-192: grid ``(ceil(N/64), B*H)``, 128 threads, the argument order of the kernel signature).
+``oracle/build_ref.py --triton`` compiles ``_triton_mixed_sparse_attn_fwd_kernel``
+(ops/pit_sparse_flash_attention_v2.py:48-153) and ``_triton_block_sparse_attn_fwd_kernel``
+(ops/block_sparse_flash_attention.py:29-112) of the reference ahead of time into ``oracle/_ref``;
+this module loads those binaries through the CUDA driver API and launches them the way the
+reference's launchers do (grid ``(ceil(N/64), B*H)``, 128 threads, the argument order of the kernel
+signature: v2 :156-192, block-sparse :115-148).
 The GPU parity tests compare the product kernel with its output.  Nothing here is used by the library.
 """
 from __future__ import annotations
@@ -16,20 +18,21 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CUBIN = os.path.join(HERE, "_ref", "ref_triton_vs_fwd.cubin")
+CUBIN_BLOCK_SPARSE = os.path.join(HERE, "_ref", "ref_triton_bs_fwd.cubin")
 
 _CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
 
 
-def available() -> bool:
-    return os.path.exists(CUBIN) and os.path.exists(CUBIN[:-6] + ".json")
+def available(cubin: str = CUBIN) -> bool:
+    return os.path.exists(cubin) and os.path.exists(cubin[:-6] + ".json")
 
 
 class ReferenceTritonKernel:
-    def __init__(self):
-        self.meta = json.load(open(CUBIN[:-6] + ".json"))
+    def __init__(self, cubin: str = CUBIN):
+        self.meta = json.load(open(cubin[:-6] + ".json"))
         self.cu = ctypes.CDLL("libcuda.so.1")
         torch.zeros(1, device="cuda")                      # makes the primary context current on this thread
-        image = open(CUBIN, "rb").read()
+        image = open(cubin, "rb").read()
         self._image = ctypes.create_string_buffer(image, len(image))
         self.module = ctypes.c_void_p()
         self._ok(self.cu.cuModuleLoadData(ctypes.byref(self.module), self._image), "cuModuleLoadData")
@@ -43,18 +46,15 @@ class ReferenceTritonKernel:
         if rc != 0:
             raise RuntimeError(f"{what} failed with CUDA driver error {rc}")
 
-    def __call__(self, q, k, v, seqlens, block_count, block_offset, column_count, column_index, sm_scale):
-        """Same tensors as ``_triton_mixed_sparse_attention`` (:156-168): ``q, k, v [B,H,N,128]`` bf16 with N a
-        multiple of 64 and equal head counts, int32 index tensors in the reference format."""
+    def launch(self, q, k, v, sm_scale, index_tensors: dict, sizes: dict):
+        """``q, k, v [B,H,N,128]`` bf16, N a multiple of 64, equal head counts; ``index_tensors`` the int32
+        pointer arguments by name, ``sizes`` the remaining integer arguments by name."""
         assert q.shape == k.shape == v.shape and q.shape[2] % 64 == 0 and q.shape[3] == 128 and q.dtype == torch.bfloat16
         o = torch.zeros_like(q)
-        values = {
-            "Q": q.data_ptr(), "K": k.data_ptr(), "V": v.data_ptr(), "seqlens": seqlens.data_ptr(), "sm_scale": float(sm_scale),
-            "block_count": block_count.data_ptr(), "block_offset": block_offset.data_ptr(),
-            "column_count": column_count.data_ptr(), "column_index": column_index.data_ptr(), "Out": o.data_ptr(),
-            "Z": q.shape[0], "H": q.shape[1], "N_CTX": q.shape[2],
-            "NUM_ROWS": block_count.shape[-1], "NNZ_S": block_offset.shape[-1], "NNZ_V": column_index.shape[-1],
-        }
+        values = {"Q": q.data_ptr(), "K": k.data_ptr(), "V": v.data_ptr(), "Out": o.data_ptr(), "sm_scale": float(sm_scale),
+                  "Z": q.shape[0], "H": q.shape[1], "N_CTX": q.shape[2]}
+        values.update({name: t.data_ptr() for name, t in index_tensors.items()})
+        values.update(sizes)
         for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
             for axis, st in zip(("z", "h", "m" if name in ("q", "o") else "n", "k"), t.stride()):
                 values[f"stride_{name}{axis}"] = st
@@ -62,13 +62,20 @@ class ReferenceTritonKernel:
         for name, ty in self.meta["params"]:
             val = values[name]
             holders.append(ctypes.c_void_p(val) if ty.startswith("*") else ctypes.c_float(val) if ty == "fp32" else ctypes.c_int32(val))
-        holders += [ctypes.c_void_p(0), ctypes.c_void_p(0)]       # global / profile scratch: sizes are 0 for this kernel
+        holders += [ctypes.c_void_p(0), ctypes.c_void_p(0)]       # global / profile scratch: sizes are 0 for these kernels
         argv = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         self._ok(self.cu.cuLaunchKernel(self.func, (q.shape[2] + 63) // 64, q.shape[0] * q.shape[1], 1,
                                         32 * int(self.meta["num_warps"]), 1, 1, int(self.meta["shared"]), stream, argv, None),
                  "cuLaunchKernel")
         return o
+
+    def __call__(self, q, k, v, seqlens, block_count, block_offset, column_count, column_index, sm_scale):
+        """Same tensors as ``_triton_mixed_sparse_attention`` (:156-168), index tensors in the reference format."""
+        return self.launch(q, k, v, sm_scale,
+                           {"seqlens": seqlens, "block_count": block_count, "block_offset": block_offset,
+                            "column_count": column_count, "column_index": column_index},
+                           {"NUM_ROWS": block_count.shape[-1], "NNZ_S": block_offset.shape[-1], "NNZ_V": column_index.shape[-1]})
 
 
 def reference_vertical_slash_attention(kernel: ReferenceTritonKernel, q, k, v, block_count, block_offset, column_count,
@@ -83,4 +90,22 @@ def reference_vertical_slash_attention(kernel: ReferenceTritonKernel, q, k, v, b
     vp = torch.nn.functional.pad(v.repeat_interleave(rep, 1), [0, 0, 0, pad]).contiguous()
     seqlens = torch.tensor([N] * B, dtype=torch.int32, device=q.device)
     out = kernel(qp, kp, vp, seqlens, block_count, block_offset, column_count, column_index, D ** -0.5)
+    return out[:, :, :N]
+
+
+def reference_block_sparse_attention(kernel: ReferenceTritonKernel, q, k, v, block_index):
+    """The reference's ``block_sparse_attention`` around its kernel (ops/block_sparse_flash_attention.py:169-186):
+    pad the sequence by ``64 - (N & 63)`` rows (a whole block when N is a multiple of 64, :178), repeat K/V to the
+    query head count, ``sm_scale = d**-0.5``, slice back.  ``block_index [B,H,rows_pad,top_k]`` is given by the
+    caller (sorted block ids; the kernel consumes the first ``min(m+1, top_k)`` of row m, :81)."""
+    B, H, N, D = q.shape
+    pad = 64 - (N & 63)
+    rep = H // k.shape[1]
+    qp = torch.nn.functional.pad(q, [0, 0, 0, pad]).contiguous()
+    kp = torch.nn.functional.pad(k.repeat_interleave(rep, 1), [0, 0, 0, pad]).contiguous()
+    vp = torch.nn.functional.pad(v.repeat_interleave(rep, 1), [0, 0, 0, pad]).contiguous()
+    assert block_index.shape[2] == qp.shape[2] // 64
+    seqlens = torch.tensor([N] * B, dtype=torch.int32, device=q.device)
+    out = kernel.launch(qp, kp, vp, D ** -0.5, {"seqlens": seqlens, "block_index": block_index.contiguous()},
+                        {"NUM_ROWS": block_index.shape[-2], "MAX_BLOCKS_PRE_ROW": block_index.shape[-1]})
     return out[:, :, :N]

@@ -235,6 +235,27 @@ def test_attention_matches_reference_triton_kernel_on_gpu(dev, n, hq, hkv, nv, n
     assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
 
 
+@pytest.mark.parametrize("n,hq,hkv,top_k", [(2048, 4, 2, 8), (1000, 2, 1, 5), (4096, 2, 2, 100)])
+def test_block_sparse_matches_reference_triton_kernel_on_gpu(dev, n, hq, hkv, top_k):
+    """The reference's block-sparse kernel (ahead-of-time build) on the block index of the product planner."""
+    from oracle import ref_triton
+
+    if not ref_triton.available(ref_triton.CUBIN_BLOCK_SPARSE):
+        pytest.skip("the reference's block-sparse Triton kernel was not compiled (oracle/_ref/ref_triton_bs_fwd.cubin)")
+    from minference_b200.ops.block_sparse_flash_attention import _build_block_index, block_sparse_attention
+    from minference_b200.synthetic import make_qkv
+
+    q, k, v = (t.to(dev) for t in make_qkv(n, hq, hkv, seed=32, dtype=torch.bfloat16))
+    bidx = _build_block_index(q, k, top_k)
+    ref = ref_triton.reference_block_sparse_attention(ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_BLOCK_SPARSE),
+                                                      q, k, v, bidx).float()
+    out = block_sparse_attention(q, k, v, top_k).float()
+    torch.cuda.synchronize()
+    d = (out - ref).abs()
+    assert torch.isfinite(ref).all() and ref.abs().max().item() > 0.1
+    assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
+
+
 def test_attention_accepts_strided_layout_and_repeated_kv(dev):
     """[B,N,H,D] memory viewed as [B,H,N,D] (the layout HF projections produce) and K/V already
     repeated to the query head count, as the reference's caller passes them."""
