@@ -58,6 +58,11 @@ class ReferenceTritonKernel:
         for name, t in (("q", q), ("k", k), ("v", v), ("o", o)):
             for axis, st in zip(("z", "h", "m" if name in ("q", "o") else "n", "k"), t.stride()):
                 values[f"stride_{name}{axis}"] = st
+        self.launch_raw(values, ((q.shape[2] + 63) // 64, q.shape[0] * q.shape[1]))
+        return o
+
+    def launch_raw(self, values: dict, grid):
+        """Launch with every kernel argument given by name (device addresses for pointers)."""
         holders = []
         for name, ty in self.meta["params"]:
             val = values[name]
@@ -65,10 +70,8 @@ class ReferenceTritonKernel:
         holders += [ctypes.c_void_p(0), ctypes.c_void_p(0)]       # global / profile scratch: sizes are 0 for these kernels
         argv = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        self._ok(self.cu.cuLaunchKernel(self.func, (q.shape[2] + 63) // 64, q.shape[0] * q.shape[1], 1,
-                                        32 * int(self.meta["num_warps"]), 1, 1, int(self.meta["shared"]), stream, argv, None),
-                 "cuLaunchKernel")
-        return o
+        self._ok(self.cu.cuLaunchKernel(self.func, int(grid[0]), int(grid[1]), 1, 32 * int(self.meta["num_warps"]), 1, 1,
+                                        int(self.meta["shared"]), stream, argv, None), "cuLaunchKernel")
 
     def __call__(self, q, k, v, seqlens, block_count, block_offset, column_count, column_index, sm_scale):
         """Same tensors as ``_triton_mixed_sparse_attention`` (:156-168), index tensors in the reference format."""
@@ -109,3 +112,46 @@ def reference_block_sparse_attention(kernel: ReferenceTritonKernel, q, k, v, blo
     out = kernel.launch(qp, kp, vp, D ** -0.5, {"seqlens": seqlens, "block_index": block_index.contiguous()},
                         {"NUM_ROWS": block_index.shape[-2], "MAX_BLOCKS_PRE_ROW": block_index.shape[-1]})
     return out[:, :, :N]
+
+
+def streaming_available() -> bool:
+    return all(available(os.path.join(HERE, "_ref", f"ref_triton_stream_{stage}_{par}.cubin"))
+               for stage in ("window", "sink", "single") for par in ("even", "ragged"))
+
+
+def reference_streaming_forward(q, k, v, n_init: int, n_local: int):
+    """The reference's ``streaming_forward`` (ops/streaming_kernel.py:611-646) with its own kernel ``_attn_fwd``:
+    a window stage over all keys and, when the sequence is longer than the window, a second stage over the first
+    ``n_init`` keys with the complement mask, fp32 O / M / L carried between the stages (:531-598, :420-499)."""
+    B, H, N, D = q.shape
+    assert n_init % 64 == 0, "only the compile-time variants with a sink count that is a multiple of 64 were built"
+    rep = H // k.shape[1]
+    q = q.contiguous()
+    k = k.repeat_interleave(rep, 1).contiguous()          # the reference asserts q.shape == k.shape (:619)
+    v = v.repeat_interleave(rep, 1).contiguous()
+    round_len = (N + 63) // 64 * 64
+    o = torch.empty((B, H, round_len, D), dtype=torch.float32, device=q.device)
+    m = torch.empty((B, H, round_len), dtype=torch.float32, device=q.device)
+    l = torch.empty((B, H, round_len), dtype=torch.float32, device=q.device)
+    par = "even" if N % 64 == 0 else "ragged"
+
+    def stage(tag, kk, vv):
+        kern = ReferenceTritonKernel(os.path.join(HERE, "_ref", f"ref_triton_stream_{tag}_{par}.cubin"))
+        values = {"Q": q.data_ptr(), "K": kk.data_ptr(), "V": vv.data_ptr(), "sm_scale": D ** -0.5,
+                  "M": m.data_ptr(), "Out": o.data_ptr(), "L": l.data_ptr(),
+                  "Z": B, "H": H, "H_KV": kk.shape[1], "N_CTX": N, "ROUND_CTX": round_len, "NKV_CTX": kk.shape[2],
+                  "sliding_window_offset": 0, "sliding_window_size": int(n_local)}
+        for name, t, axes in (("q", q, "zhmk"), ("k", kk, "zhnk"), ("v", vv, "zhkn"), ("o", o, "zhmn")):
+            for axis, st in zip(axes, t.stride()):
+                values[f"stride_{name}{axis}"] = st
+        kern.launch_raw(values, ((N + 63) // 64, B * H))
+        return kern
+
+    keep = []
+    if N > n_local:
+        keep.append(stage("window", k, v))
+        keep.append(stage("sink", k[:, :, :n_init].contiguous(), v[:, :, :n_init].contiguous()))
+    else:
+        keep.append(stage("single", k, v))
+    torch.cuda.synchronize()          # the modules in `keep` must outlive their launches
+    return o[:, :, :N].to(q.dtype)

@@ -256,6 +256,25 @@ def test_block_sparse_matches_reference_triton_kernel_on_gpu(dev, n, hq, hkv, to
     assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
 
 
+@pytest.mark.parametrize("n,n_init,n_local", [(2048, 128, 512), (1000, 64, 200), (1024, 128, 4096), (3000, 128, 1000)])
+def test_streaming_matches_reference_triton_kernel_on_gpu(dev, n, n_init, n_local):
+    """The reference's streaming (A-shape) kernel, both of its stages, against the one-pass product kernel."""
+    from oracle import ref_triton
+
+    if not ref_triton.streaming_available():
+        pytest.skip("the reference's streaming Triton kernel was not compiled (oracle/_ref/ref_triton_stream_*.cubin)")
+    from minference_b200.ops.streaming_kernel import streaming_forward
+    from minference_b200.synthetic import make_qkv
+
+    q, k, v = (t.to(dev) for t in make_qkv(n, 4, 2, seed=33, dtype=torch.bfloat16))
+    ref = ref_triton.reference_streaming_forward(q, k, v, n_init, n_local).float()
+    out = streaming_forward(q, k, v, n_init, n_local).float()
+    torch.cuda.synchronize()
+    d = (out - ref).abs()
+    assert torch.isfinite(ref).all() and ref.abs().max().item() > 0.1
+    assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
+
+
 def test_attention_accepts_strided_layout_and_repeated_kv(dev):
     """[B,N,H,D] memory viewed as [B,H,N,D] (the layout HF projections produce) and K/V already
     repeated to the query head count, as the reference's caller passes them."""
