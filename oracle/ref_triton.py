@@ -19,6 +19,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 CUBIN = os.path.join(HERE, "_ref", "ref_triton_vs_fwd.cubin")
 CUBIN_BLOCK_SPARSE = os.path.join(HERE, "_ref", "ref_triton_bs_fwd.cubin")
+CUBIN_128K_8HEADS = os.path.join(HERE, "_ref", "ref_triton_vs_fwd_128k_8heads.cubin")   # specialised like a JIT call
 
 _CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
 
@@ -63,6 +64,9 @@ class ReferenceTritonKernel:
 
     def launch_raw(self, values: dict, grid):
         """Launch with every kernel argument given by name (device addresses for pointers)."""
+        for name, val in self.meta.get("example_ints", {}).items():       # a binary specialised for fixed sizes
+            if values[name] != val:
+                raise ValueError(f"this build of the kernel was specialised for {name}={val}, got {values[name]}")
         holders = []
         for name, ty in self.meta["params"]:
             val = values[name]

@@ -275,6 +275,53 @@ def test_streaming_matches_reference_triton_kernel_on_gpu(dev, n, n_init, n_loca
     assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (d.max().item(), d.mean().item())
 
 
+def test_reference_triton_kernel_timing_131072(dev, capsys):
+    """Same 131072-token vertical-slash inputs (8 query / 2 KV heads) through the reference's own Triton
+    kernel and the product kernel: outputs agree, and the CUDA-event times of both are printed
+    (run with -s to see them; the reference kernel gets K/V already repeated and its dense index tables)."""
+    from oracle import ref_triton
+
+    if not ref_triton.available():
+        pytest.skip("the reference's Triton kernel was not compiled (oracle/_ref/ref_triton_vs_fwd.cubin)")
+    from minference_b200.cuda import convert_vertical_slash_indexes
+    from minference_b200.modules.minference_forward import vertical_slash_estimate
+    from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import make_qkv
+
+    n, hq, hkv = 131072, 8, 2
+    q, k, v = make_qkv(n, hq, hkv, seed=0, dtype=torch.bfloat16, device=dev)
+    v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, 1000, 6096)
+    plan = build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)
+    bc, bo, cc, ci = convert_vertical_slash_indexes(torch.tensor([n], dtype=torch.int32, device=dev), v_idx, s_idx, n)
+    # the build specialised for exactly these sizes (what the JIT does: unit strides folded, divisibility hints)
+    kernel = ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_128K_8HEADS if ref_triton.available(ref_triton.CUBIN_128K_8HEADS)
+                                              else ref_triton.CUBIN)
+    kr, vr = k.repeat_interleave(hq // hkv, 1).contiguous(), v.repeat_interleave(hq // hkv, 1).contiguous()
+    seqlens = torch.tensor([n], dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), out
+
+    t_ref, ref = timed(lambda: kernel(q, kr, vr, seqlens, bc, bo, cc, ci, 128 ** -0.5))
+    t_new, out = timed(lambda: sparse_attention_forward(q, k, v, plan))
+    tiles = plan.count_tiles()
+    d = (out.float() - ref.float()).abs()
+    with capsys.disabled():
+        print(f"\n131072 tokens, {hq}/{hkv} heads, {tiles} tiles: reference Triton kernel {t_ref:.1f} ms "
+              f"({tiles * 2097152 / t_ref / 1e9:.0f} TFLOP/s), product kernel {t_new:.1f} ms "
+              f"({tiles * 2097152 / t_new / 1e9:.0f} TFLOP/s), ratio {t_ref / t_new:.2f}; max-abs difference {d.max().item():.2e}")
+    assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS
+    assert t_new < t_ref
+
+
 def test_attention_accepts_strided_layout_and_repeated_kv(dev):
     """[B,N,H,D] memory viewed as [B,H,N,D] (the layout HF projections produce) and K/V already
     repeated to the query head count, as the reference's caller passes them."""
