@@ -460,16 +460,33 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (t == INT32_MAX) break;
                 unsigned long long mk[4][2];
                 unsigned long long any_hi = 0ull;
+                // inside long ranges every live row block covers [t, t+128) entirely and runs on: no mask arithmetic
+                bool whole = true;
+                bool lv[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    mk[r][0] = 0ull; mk[r][1] = 0ull;
-                    while (cur[r].live() && cur[r].a < t + 128) {      // every range of the row block inside [t, t+128)
-                        const int hi = min(cur[r].b, t + 128);
-                        span128(cur[r].a - t, hi - t, mk[r][0], mk[r][1]);
-                        if (cur[r].b <= t + 128) { ++cur[r].ri; cur[r].fetch(lane); }
-                        else { cur[r].a = t + 128; break; }
+                    lv[r] = cur[r].live();
+                    whole = whole && (!lv[r] || (cur[r].a == t && cur[r].b > t + 128));
+                }
+                if (whole) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        mk[r][0] = mk[r][1] = lv[r] ? ~0ull : 0ull;
+                        if (lv[r]) cur[r].a = t + 128;
                     }
-                    any_hi |= mk[r][1];
+                    any_hi = ~0ull;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        mk[r][0] = 0ull; mk[r][1] = 0ull;
+                        while (cur[r].live() && cur[r].a < t + 128) {      // every range of the row block inside [t, t+128)
+                            const int hi = min(cur[r].b, t + 128);
+                            span128(cur[r].a - t, hi - t, mk[r][0], mk[r][1]);
+                            if (cur[r].b <= t + 128) { ++cur[r].ri; cur[r].fetch(lane); }
+                            else { cur[r].a = t + 128; break; }
+                        }
+                        any_hi |= mk[r][1];
+                    }
                 }
                 const int width = any_hi ? 128 : 64;
                 if (!publish(kTileStep, t, width, mk)) break;
