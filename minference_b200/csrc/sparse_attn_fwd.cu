@@ -350,7 +350,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 *reinterpret_cast<int4*>(&st) = make_int4(kind, t, width, parts);
                 issued += (unsigned)(__popc(parts) * (width >> 5));     // a slot is two row blocks tall
 #pragma unroll
-                for (int r = 0; r < 4; ++r) { st.mask[r][0] = mk[r][0]; st.mask[r][1] = mk[r][1]; }
+                for (int r = 0; r < 4; ++r)       // one 16-byte store per row block
+                    *reinterpret_cast<ulonglong2*>(&st.mask[r][0]) = make_ulonglong2(mk[r][0], mk[r][1]);
                 mbar_arrive(bar(&ctl->m_full[step % kNM]));
 #ifdef MINF_TIMELINE
                 if (kind != kEndStep) {
@@ -622,12 +623,14 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 const uint32_t d = tmem + slot * 256 + 128;
                 const uint32_t a_lo = ((smem_base + kQOff + slot * kTile) >> 4) | (1u << 16);
                 const uint32_t b_lo = ((smem_base + kKOff + (j % kNK) * kTile) >> 4) | (1u << 16);
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
-                    if (elect_one()) umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t adv = (kk >> 2) * (16384 >> 4) + (kk & 3) * (32 >> 4);
+                        umma_ss(d, desc(a_lo + adv), desc(b_lo + adv), idesc, kk > 0);
+                    }
+                    umma_commit(bar(&ctl->s_full[slot]));
                 }
-                if (elect_one()) umma_commit(bar(&ctl->s_full[slot]));
             };
             int npv[2] = {0, 0};
             // PV product of one half of a step's keys (P arrives in two halves, see softmax_row)
@@ -637,17 +640,19 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 const uint32_t p = tmem + slot * 256 + 128;
                 const uint32_t b_lo = ((smem_base + kVOff + kv * kTile) >> 4) | ((16384u >> 4) << 16);
                 const uint32_t acc0 = (npv[slot] > 0 || half > 0) ? 1u : 0u;
-                if (width == 128) {
+                if (elect_one()) {
+                    if (width == 128) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int kk = 4 * half + i;
-                        if (elect_one()) umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
-                    }
-                } else {
+                        for (int i = 0; i < 4; ++i) {
+                            const int kk = 4 * half + i;
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                        }
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int kk = 2 * half + i;
-                        if (elect_one()) umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                        for (int i = 0; i < 2; ++i) {
+                            const int kk = 2 * half + i;
+                            umma_ts(d, p + kk * 8, desc(b_lo + kk * (2048 >> 4)), idesc, i > 0 ? 1u : acc0);
+                        }
                     }
                 }
                 if (half == 1) ++npv[slot];
