@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// ---------------------------------------------------------------- TMA (tile mode, no multicast)
+// ---------------------------------------------------------------- TMA (tile mode, one destination CTA)
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {
     asm volatile(
