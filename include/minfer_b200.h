@@ -29,7 +29,7 @@ extern "C" {
 #define MINF_E_CUDA (-2)     /* CUDA runtime / driver error at launch */
 #define MINF_E_UNSUPPORTED (-3)
 
-/* status[] words written by the kernels (caller provides int32_t status[MINF_STATUS_WORDS]) */
+/* status[] words written by the kernels (caller provides int32_t status[MINF_STATUS_WORDS], 8-byte aligned) */
 #define MINF_STATUS_WORDS 4
 #define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan */
 #define MINF_ST_NO_SLASH 1   /* number of row blocks whose slash list has no offset < end row */

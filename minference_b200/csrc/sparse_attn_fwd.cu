@@ -897,6 +897,7 @@ extern "C" int minf_sparse_attention_fwd_window(
                     q_pos0, n_q, kv_pos0, n_kv, context_size);
     if ((q_pos0 % 256) || (kv_pos0 % 64))
         return fail(MINF_E_ARG, "q_pos0 must be a multiple of 256 and kv_pos0 a multiple of 64");
+    if (reinterpret_cast<uintptr_t>(status) & 7) return fail(MINF_E_ARG, "status must be 8-byte aligned (words 2-3 are updated as one 64-bit counter)");
     if (head_mode && !head_param) return fail(MINF_E_ARG, "head_mode given without head_param");
     if (!head_mode && !plan) return fail(MINF_E_ARG, "plan is required when every head uses it");
     if ((reinterpret_cast<uintptr_t>(o) & 15) || (o_strides[0] % 8) || (o_strides[1] % 8) || (o_strides[2] % 8))
