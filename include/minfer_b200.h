@@ -31,7 +31,10 @@ extern "C" {
 
 /* status[] words written by the kernels (caller provides int32_t status[MINF_STATUS_WORDS], 8-byte aligned) */
 #define MINF_STATUS_WORDS 4
-#define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan */
+#define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan (a head in
+                                plan mode without a plan, a range count beyond the slot's capacity, ranges that are
+                                not ascending and disjoint, or marked columns without a vertical list; the affected
+                                row blocks are computed from the part of the plan read before the fault) */
 #define MINF_ST_NO_SLASH 1   /* number of row blocks whose slash list has no offset < end row */
 #define MINF_ST_AUX0 2        /* words 2-3, read as one uint64: 64x64 tile equivalents the attention kernel sent  */
 #define MINF_ST_AUX1 3        /* to the tensor pipe (its 128-row x 64/128-key steps), summed over launches         */
@@ -227,10 +230,17 @@ int minf_sparse_attention_fwd(
  * log2(e)) over the keys this call saw (-inf when it saw none); the output rows are normalised
  * with that sum, so partial results of several key chunks combine as
  *   o = sum_i 2^(lse_i - lse) * o_i,   lse = log2(sum_i 2^lse_i).
- * No counterpart in the reference (it has no sequence parallelism).
+ * The kernel does that combination itself when the carry pair is given: `o_acc` (fp32
+ * [batch, hq, n_q, 128], contiguous, 16-byte aligned) and `lse_acc` (fp32 [batch, hq, n_q]) hold the
+ * merged, normalised result of the key chunks seen so far and its log-sum-exp.  The caller fills
+ * lse_acc with -inf before the first call (o_acc need not be initialised: a row whose lse_acc is
+ * -inf is not read); every call folds its keys in, in fp32, and rewrites both.  With a carry `o` may
+ * be NULL; when given it receives the merged result rounded to bf16 (pass it with the last key
+ * chunk of a query chunk, so the output is rounded once).  Calls that share a carry must be ordered
+ * on one stream.  No counterpart in the reference (it has no sequence parallelism).
  */
 int minf_sparse_attention_fwd_window(
-    const void* q, const void* k, const void* v, void* o, float* lse,
+    const void* q, const void* k, const void* v, void* o, float* lse, float* o_acc, float* lse_acc,
     const int64_t q_strides[3], const int64_t k_strides[3],
     const int64_t v_strides[3], const int64_t o_strides[3],
     int batch, int hq, int hkv, int context_size, int n_q, int q_pos0, int n_kv, int kv_pos0,

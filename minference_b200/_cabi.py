@@ -50,7 +50,7 @@ SIGNATURES = {
                                 [c_int, c_int] + [c_void_p] * 4 + [c_void_p, c_void_p]),
     "minf_sparse_attention_fwd": (c_int, [c_void_p] * 4 + [_I64x3] * 4 + [c_int] * 5 + [c_float] +
                                   [c_void_p] * 4 + [c_int, c_int] + [c_void_p, c_void_p]),
-    "minf_sparse_attention_fwd_window": (c_int, [c_void_p] * 5 + [_I64x3] * 4 + [c_int] * 9 + [c_float] +
+    "minf_sparse_attention_fwd_window": (c_int, [c_void_p] * 7 + [_I64x3] * 4 + [c_int] * 9 + [c_float] +
                                          [c_void_p] * 4 + [c_int, c_int] + [c_void_p, c_void_p]),
     "minf_plan_count_tiles": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p]),
     "minf_plan_count_tiles_window": (c_int, [c_void_p] + [c_int] * 6 + [c_void_p, c_void_p]),
@@ -113,7 +113,8 @@ def raise_on_status(status: torch.Tensor, what: str) -> None:
     st = status.tolist()
     if st[ST_ERROR]:
         raise MInferB200Error(f"{what}: device reported error bits {st[ST_ERROR]:#x} "
-                              "(1 = abandoned wait, 2 = misaligned shared memory)")
+                              "(1 = abandoned wait, 2 = misaligned shared memory, 4 = bad plan: a plan-mode head without a plan, "
+                              "a range count beyond the slot's capacity, unordered ranges, or columns without a vertical list)")
     if st[ST_NO_SLASH]:
         raise MInferB200Error(f"{what}: {st[ST_NO_SLASH]} row blocks have no slash offset below their last row; "
                               "s_idx must contain an offset < 64")

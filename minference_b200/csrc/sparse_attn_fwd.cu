@@ -78,6 +78,8 @@ struct AttnArgs {
     const __nv_bfloat16* k;
     const __nv_bfloat16* v;
     float* lse;                       // optional [batch, hq, n_q], base-2 log-sum-exp of the scaled logits
+    float* o_acc;                     // optional carry [batch, hq, n_q, 128] fp32: merged, normalised output so far
+    float* lse_acc;                   // its log-sum-exp [batch, hq, n_q]; -inf = nothing accumulated yet
     long long o_sb, o_sh, o_sn;
     long long k_sb, k_sh, k_sn;
     long long v_sb, v_sh, v_sn;
@@ -108,6 +110,8 @@ struct RangeCursor {
     int2 buf;
     int a, b;
     int last_row, kv_lo, kv_hi;
+    int floor_end;      // end of the previous range: a plan whose ranges are not ascending and disjoint is refused
+    bool bad;
     __device__ __forceinline__ void fetch(int lane) {
         for (;;) {
             if (ri >= n) { a = INT32_MAX; b = INT32_MAX; return; }
@@ -115,14 +119,22 @@ struct RangeCursor {
                 base = ri;
                 buf = (base + lane < n) ? rng[base + lane] : make_int2(INT32_MAX, INT32_MAX);
             }
-            a = max(__shfl_sync(0xffffffffu, buf.x, ri - base), kv_lo);
-            b = min(__shfl_sync(0xffffffffu, buf.y, ri - base), kv_hi);
+            const int ra = __shfl_sync(0xffffffffu, buf.x, ri - base);
+            const int rb = __shfl_sync(0xffffffffu, buf.y, ri - base);
+            if (ra < floor_end || rb <= ra) {    // not a plan this library wrote: stop here instead of wandering
+                bad = true; ri = n; a = INT32_MAX; b = INT32_MAX;
+                return;
+            }
+            floor_end = rb;
+            a = max(ra, kv_lo);
+            b = min(rb, kv_hi);
             if (a < b || a >= kv_hi) return;     // usable, or everything from here on lies past the window
             ++ri;                                // range entirely before the window
         }
     }
     __device__ __forceinline__ void init(const int2* r, int count, int first, int last, int lo, int hi, int lane) {
         rng = r; n = count; ri = first; base = -64; last_row = last; kv_lo = lo; kv_hi = hi;
+        floor_end = INT32_MIN; bad = false;
         fetch(lane);
     }
     __device__ __forceinline__ bool live() const { return ri < n && a <= last_row && a < kv_hi; }
@@ -142,49 +154,19 @@ __device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigne
     w1 = below64(lim + 1 - 64);
 }
 
-#ifdef MINF_TIMELINE
-// Debug builds only: cycle stamps of one CTA's warps, read back by a probe script.
-__device__ unsigned long long g_step_stats[8];   // slot-steps: tile128, tile64, gather128, gather64
-__device__ long long* g_timeline = nullptr;
-__device__ int g_timeline_block = 0;
-#define TL(ev, step)                                                                               \
-    do {                                                                                           \
-        if (tl_ptr) {                                                                              \
-            uint32_t c_;                                                                           \
-            asm volatile("mov.u32 %0, %%clock;" : "=r"(c_));                                       \
-            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(tl_ptr + 1 + tl_n), "r"(c_),     \
-                         "r"((uint32_t)(ev) | ((uint32_t)(step) << 8)));                           \
-            ++tl_n;                                                                                \
-        }                                                                                          \
-    } while (0)
-#define TL_DECL                                                                                    \
-    long long* tl_ptr = (g_timeline && (int)blockIdx.x == g_timeline_block && (threadIdx.x & 31) == 0) \
-                            ? g_timeline + (threadIdx.x >> 5) * 8192 : nullptr;                    \
-    int tl_n = 0;
-#define TL_FLUSH do { if (tl_ptr) tl_ptr[0] = tl_n; } while (0)
-#define TL_PARAMS , long long* tl_ptr, int& tl_n, int tl_step
-#define TL_ARGS(j) , tl_ptr, tl_n, (j)
-#else
-#define TL_PARAMS
-#define TL_ARGS(j)
-#define TL(ev, step) do { } while (0)
-#define TL_DECL
-#define TL_FLUSH do { } while (0)
-#endif
-
 // One softmax step of one query row: S (fp32, NCH*32 columns at t_s) -> P (bf16 pairs written
 // back over the first NCH*16 columns).  The whole row is held in registers, so TMEM is read
-// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.
+// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.  A 32-key chunk that no row of
+// the warp can see (the other row block's half of an isolated diagonal, keys past the causal
+// limit) is neither loaded nor exponentiated: its P is written as zeros.
 template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,
-                                            uint32_t bar_half0, uint32_t bar_half1 TL_PARAMS) {
-#ifdef MINF_PROBE_NOSOFTMAX   // timing probe only (wrong numbers): the MMA warp's own pace
-    tc_fence_before();
-    mbar_arrive(bar_half0);
-    mbar_arrive(bar_half1);
-    return;
-#endif
+                                            uint32_t bar_half0, uint32_t bar_half1) {
+    // bit c set <=> some row of this warp sees a key of chunk c (TMEM loads are warp-collective)
+    uint32_t live = ((uint32_t)m0 != 0u ? 1u : 0u) | ((uint32_t)(m0 >> 32) != 0u ? 2u : 0u);
+    if (NCH == 4) live |= ((uint32_t)m1 != 0u ? 4u : 0u) | ((uint32_t)(m1 >> 32) != 0u ? 8u : 0u);
+    live = __reduce_or_sync(0xffffffffu, live);
     // The row maximum of a chunk is taken while the next chunk's load is in flight.
     uint32_t sr[NCH][32];
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -193,17 +175,18 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
     for (int c = 0; c < NCH; ++c) {
         tmem_wait_ld();
         if (c + 1 < NCH) tmem_ld32(t_s + 32 * (c + 1), sr[c + 1]);
-        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
-        if (cm != 0xffffffffu) {
+        if ((live >> c) & 1u) {
+            const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+            if (cm != 0xffffffffu) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
+                for (int i = 0; i < 32; ++i)
+                    if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+                mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 2)
-            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
     }
-    TL(40, tl_step);
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
     float alpha = 1.f;
     if (mx > m_ref + 8.f) {          // raise the reference maximum only on a jump of more than 2^8
@@ -212,7 +195,6 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
         m_ref = mx;
     }
     const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-    TL(41, tl_step);
     // O of this slot is at rest here: the QK^T that filled S was issued after the previous PV
     if (have_o && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
@@ -233,20 +215,20 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         uint32_t pk[16];
+        if ((live >> c) & 1u) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2), x0, x1);
-#ifdef MINF_PROBE_NOEXP   // timing probe only (wrong numbers): how much of the step is the MUFU?
-            const float p0 = x0, p1 = x1;
-#else
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-#endif
-            ps2[(i >> 1) & 3] = add_f32x2(ps2[(i >> 1) & 3], pack_f32x2(p0, p1));
-            pk[i >> 1] = pack_bf16x2(p0, p1);
+            for (int i = 0; i < 32; i += 2) {
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2), x0, x1);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                ps2[(i >> 1) & 3] = add_f32x2(ps2[(i >> 1) & 3], pack_f32x2(p0, p1));
+                pk[i >> 1] = pack_bf16x2(p0, p1);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = 0u;
         }
         tmem_st16(t_s + 16 * c, pk);
-        TL(42 + c, tl_step);
         if (c == NCH / 2 - 1) {
             tmem_wait_st();
             tc_fence_before();
@@ -267,7 +249,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
     Control* ctl = reinterpret_cast<Control*>(smem + kCtlOff);
     const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    TL_DECL
 
     // Block order: one KV head at a time (its query heads and all their items, latest rows = most
     // work first), so that the CTAs in flight stream the same K/V and find it in L2; the K and V
@@ -336,6 +317,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         int step = 0;
         unsigned issued = 0;           // 64x64 tile equivalents this CTA sends to the tensor pipe
         bool ok = true;
+        bool bad_plan = false;         // the plan of this head cannot have been written by the plan builders
         auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
             const int s = idx % ring, use = idx / ring;
             if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
@@ -353,15 +335,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 for (int r = 0; r < 4; ++r)       // one 16-byte store per row block
                     *reinterpret_cast<ulonglong2*>(&st.mask[r][0]) = make_ulonglong2(mk[r][0], mk[r][1]);
                 mbar_arrive(bar(&ctl->m_full[step % kNM]));
-#ifdef MINF_TIMELINE
-                if (kind != kEndStep) {
-                    const int parts = ((mk[0][0] | mk[0][1] | mk[1][0] | mk[1][1]) != 0ull ? 1 : 0) + ((mk[2][0] | mk[2][1] | mk[3][0] | mk[3][1]) != 0ull ? 1 : 0);
-                    atomicAdd(&g_step_stats[(kind == kGatherStep ? 2 : 0) + (width == 128 ? 0 : 1)], (unsigned long long)parts);
-                    int live = 0;
-                    for (int r = 0; r < 4; ++r) live += __popcll(mk[r][0]) + __popcll(mk[r][1]);
-                    atomicAdd(&g_step_stats[4], (unsigned long long)live);      // visible (row block, key) pairs
-                }
-#endif
             }
             return true;
         };
@@ -376,7 +349,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 tma_load_4d(dst, m, fb, 0, lt, hk, b);
                 tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
             }
-            TL(2, step);
             if (!wait_use(ctl->v_empty, kNV, step)) return false;
             if (lane == 0) {
                 const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
@@ -386,7 +358,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 tma_load_4d(dst, m, fb, 0, lt, hk, b);
                 tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
             }
-            TL(3, step);
             return true;
         };
 
@@ -419,6 +390,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     t += width;
                 }
             }
+        } else if (a.plan == nullptr) {
+            bad_plan = true;           // a head in plan mode without a plan: no keys, reported below
         } else {
             const unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
             const int32_t* rng_cnt = reinterpret_cast<const int32_t*>(slot);
@@ -432,6 +405,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 const bool present = ml < rows_loc;
                 rp[r] = present ? rng_all + plan_rng_offset(a.layout, ml) : nullptr;
                 rn[r] = present ? rng_cnt[ml] : 0;
+                // a slot nobody wrote holds an arbitrary count: never walk past the slot's capacity
+                const int cap = min(a.layout.cap_s, a.layout.rb_base + ml + 2);
+                if (rn[r] < 0 || rn[r] > cap) { bad_plan = true; rn[r] = 0; }
                 first[r] = 0; hi_[r] = rn[r];
             }
             if (kv_lo > 0) {
@@ -494,6 +470,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!load_tile(t, width)) break;
                 ++step;
             }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) bad_plan = bad_plan || cur[r].bad;
             // ---- gathered columns: union of the row blocks' bit masks over the vertical list,
             //      restricted to columns inside the local key window
             const int words = a.layout.words_v;
@@ -573,6 +551,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     any |= wr[r];
                 }
                 if (any == 0u) continue;
+                if (vlist == nullptr) { bad_plan = true; break; }     // columns marked but no vertical list given
                 const int vi = 32 * w + lane;
                 const int colv = (((any >> lane) & 1u) && vi < a.cap_v) ? vlist[vi] : -1;
                 const unsigned sel = __ballot_sync(0xffffffffu, colv >= kv_lo && colv < kv_hi);
@@ -597,6 +576,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
                 mbar_arrive(bar(&ctl->k_full[step % kNK]));
         }
+        if (lane == 0 && bad_plan) atomicOr(a.status + MINF_ST_ERROR, 4);
         if (lane == 0 && issued)
             atomicAdd(reinterpret_cast<unsigned long long*>(a.status + MINF_ST_AUX0), (unsigned long long)issued);
     } else if (warp == 1) {
@@ -679,27 +659,22 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!ok) break;
                 const int4 nxt = read_step(j + 1);
                 const bool nxt_live = nxt.x != kEndStep;
-                TL(30, j);
                 ok = wait(&ctl->v_full[kv], kv_par);
                 if (!ok) break;
-                TL(32, j);
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
                     if ((cur.w >> s) & 1) {
                         ok = wait(&ctl->p_half[s][0], npv[s] & 1);
                         if (!ok) break;
                         tc_fence_after();
-                        TL(10 + s, j);
                         issue_pv_half(j, kv, s, cur.z, 0);
                         ok = wait(&ctl->p_half[s][1], npv[s] & 1);
                         if (!ok) break;
                         tc_fence_after();
-                        TL(14 + s, j);
                         issue_pv_half(j, kv, s, cur.z, 1);
                     }
                     if (nxt_live && ((nxt.w >> s) & 1)) {
                         issue_s(j + 1, s, nxt.z);
-                        TL(22 + s, j + 1);
                     }
                 }
                 if (!ok) break;
@@ -768,12 +743,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             ok = mbar_wait(bar(&ctl->s_full[slot]), n & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            TL(1, j);
             if (width == 128)
-                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]) TL_ARGS(j));
+                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
             else
-                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]) TL_ARGS(j));
-            TL(2, j);
+                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
             ++n;
         }
 
@@ -786,10 +759,24 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         if (warp_ok) {
             tc_fence_after();
             const bool any_key = n > 0 && m_ref != -INFINITY;   // the row saw a visible key
-            const float inv = any_key ? 1.f / l_sum : 0.f;
-            if (a.lse && row_ok)
-                a.lse[((size_t)b * a.hq + h) * a.n_q + lrow] = any_key ? m_ref + log2f(l_sum) : -INFINITY;
-            __nv_bfloat16* dst = a.o + b * a.o_sb + h * a.o_sh + (long long)lrow * a.o_sn;
+            const float lse_cur = any_key ? m_ref + log2f(l_sum) : -INFINITY;
+            const size_t row_idx = ((size_t)b * a.hq + h) * a.n_q + lrow;
+            if (a.lse && row_ok) a.lse[row_idx] = lse_cur;
+            // out = w_cur * O (unnormalised, reference maximum m_ref) + w_prev * carried output
+            float w_cur = any_key ? 1.f / l_sum : 0.f, w_prev = 0.f;
+            if (a.lse_acc && row_ok) {
+                const float lse_prev = a.lse_acc[row_idx];
+                float lse_new = lse_cur;
+                if (lse_prev != -INFINITY) {
+                    const float top = fmaxf(lse_prev, lse_cur);
+                    lse_new = top + log2f(exp2f(lse_prev - top) + exp2f(lse_cur - top));
+                    w_prev = exp2f(lse_prev - lse_new);
+                    w_cur = any_key ? exp2f(m_ref - lse_new) : 0.f;
+                }
+                a.lse_acc[row_idx] = lse_new;
+            }
+            __nv_bfloat16* dst = a.o ? a.o + b * a.o_sb + h * a.o_sh + (long long)lrow * a.o_sn : nullptr;
+            float* acc = a.o_acc ? a.o_acc + row_idx * kHeadDim : nullptr;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t orow[32];
@@ -802,20 +789,36 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
                 if (row_ok) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 out;
-                        out.x = pack_bf16x2(__uint_as_float(orow[8 * q4 + 0]) * inv, __uint_as_float(orow[8 * q4 + 1]) * inv);
-                        out.y = pack_bf16x2(__uint_as_float(orow[8 * q4 + 2]) * inv, __uint_as_float(orow[8 * q4 + 3]) * inv);
-                        out.z = pack_bf16x2(__uint_as_float(orow[8 * q4 + 4]) * inv, __uint_as_float(orow[8 * q4 + 5]) * inv);
-                        out.w = pack_bf16x2(__uint_as_float(orow[8 * q4 + 6]) * inv, __uint_as_float(orow[8 * q4 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = out;
+                    for (int q4 = 0; q4 < 4; ++q4) {        // eight output values at a time
+                        float val[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) val[i] = __uint_as_float(orow[8 * q4 + i]) * w_cur;
+                        if (w_prev != 0.f) {
+                            const float4 p0 = *reinterpret_cast<const float4*>(acc + 32 * c + 8 * q4);
+                            const float4 p1 = *reinterpret_cast<const float4*>(acc + 32 * c + 8 * q4 + 4);
+                            val[0] = fmaf(p0.x, w_prev, val[0]); val[1] = fmaf(p0.y, w_prev, val[1]);
+                            val[2] = fmaf(p0.z, w_prev, val[2]); val[3] = fmaf(p0.w, w_prev, val[3]);
+                            val[4] = fmaf(p1.x, w_prev, val[4]); val[5] = fmaf(p1.y, w_prev, val[5]);
+                            val[6] = fmaf(p1.z, w_prev, val[6]); val[7] = fmaf(p1.w, w_prev, val[7]);
+                        }
+                        if (acc) {
+                            *reinterpret_cast<float4*>(acc + 32 * c + 8 * q4) = make_float4(val[0], val[1], val[2], val[3]);
+                            *reinterpret_cast<float4*>(acc + 32 * c + 8 * q4 + 4) = make_float4(val[4], val[5], val[6], val[7]);
+                        }
+                        if (dst) {
+                            uint4 out;
+                            out.x = pack_bf16x2(val[0], val[1]);
+                            out.y = pack_bf16x2(val[2], val[3]);
+                            out.z = pack_bf16x2(val[4], val[5]);
+                            out.w = pack_bf16x2(val[6], val[7]);
+                            *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = out;
+                        }
                     }
                 }
             }
         }
     }
 
-    TL_FLUSH;
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && ctl->abort) atomicOr(a.status + MINF_ST_ERROR, 1);
@@ -861,33 +864,24 @@ int make_tmap_bhnd(CUtensorMap* tm, const void* base, int batch, int heads, int 
     return MINF_OK;
 }
 
-#ifdef MINF_TIMELINE
-extern "C" int minf_debug_step_stats(unsigned long long* out, int reset) {
-    if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(g_step_stats, z, sizeof(z)); return 0; }
-    cudaMemcpyFromSymbol(out, g_step_stats, 8 * sizeof(unsigned long long));
-    return 0;
-}
-extern "C" int minf_debug_timeline(long long* buf, int block) {
-    cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf));
-    cudaMemcpyToSymbol(g_timeline_block, &block, sizeof(block));
-    return 0;
-}
-#endif
 
 }  // namespace minf
 
 using namespace minf;
 
 extern "C" int minf_sparse_attention_fwd_window(
-    const void* q, const void* k, const void* v, void* o, float* lse,
+    const void* q, const void* k, const void* v, void* o, float* lse, float* o_acc, float* lse_acc,
     const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3], const int64_t o_strides[3],
     int batch, int hq, int hkv, int context_size, int n_q, int q_pos0, int n_kv, int kv_pos0,
     int head_dim, float sm_scale,
     const int32_t* head_mode, const int32_t* head_param,
     const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
     int32_t* status, void* stream) {
-    if (!q || !k || !v || !o || !status || !q_strides || !k_strides || !v_strides || !o_strides)
+    if (!q || !k || !v || !status || !q_strides || !k_strides || !v_strides || (o && !o_strides))
         return fail(MINF_E_ARG, "null pointer argument");
+    if (!o && !o_acc) return fail(MINF_E_ARG, "neither o nor o_acc given: the call would have no output");
+    if ((o_acc != nullptr) != (lse_acc != nullptr)) return fail(MINF_E_ARG, "o_acc and lse_acc go together");
+    if (reinterpret_cast<uintptr_t>(o_acc) & 15) return fail(MINF_E_ARG, "o_acc must be 16-byte aligned");
     if (head_dim != kHeadDim) return fail(MINF_E_UNSUPPORTED, "head_dim must be 128 (got %d)", head_dim);
     if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || context_size < 1)
         return fail(MINF_E_ARG, "bad sizes: batch=%d hq=%d hkv=%d context=%d", batch, hq, hkv, context_size);
@@ -900,7 +894,7 @@ extern "C" int minf_sparse_attention_fwd_window(
     if (reinterpret_cast<uintptr_t>(status) & 7) return fail(MINF_E_ARG, "status must be 8-byte aligned (words 2-3 are updated as one 64-bit counter)");
     if (head_mode && !head_param) return fail(MINF_E_ARG, "head_mode given without head_param");
     if (!head_mode && !plan) return fail(MINF_E_ARG, "plan is required when every head uses it");
-    if ((reinterpret_cast<uintptr_t>(o) & 15) || (o_strides[0] % 8) || (o_strides[1] % 8) || (o_strides[2] % 8))
+    if (o && ((reinterpret_cast<uintptr_t>(o) & 15) || (o_strides[0] % 8) || (o_strides[1] % 8) || (o_strides[2] % 8)))
         return fail(MINF_E_ARG, "o: base and strides must be 16-byte aligned");
     if (cap_v < 0 || cap_s < 1 || cap_v > (1 << 20)) return fail(MINF_E_ARG, "bad plan capacities");
 
@@ -916,8 +910,8 @@ extern "C" int minf_sparse_attention_fwd_window(
     a.o = static_cast<__nv_bfloat16*>(o);
     a.k = static_cast<const __nv_bfloat16*>(k);
     a.v = static_cast<const __nv_bfloat16*>(v);
-    a.lse = lse;
-    a.o_sb = o_strides[0]; a.o_sh = o_strides[1]; a.o_sn = o_strides[2];
+    a.lse = lse; a.o_acc = o_acc; a.lse_acc = lse_acc;
+    if (o) { a.o_sb = o_strides[0]; a.o_sh = o_strides[1]; a.o_sn = o_strides[2]; }
     a.k_sb = k_strides[0]; a.k_sh = k_strides[1]; a.k_sn = k_strides[2];
     a.v_sb = v_strides[0]; a.v_sh = v_strides[1]; a.v_sn = v_strides[2];
     a.batch = batch; a.hq = hq; a.hkv = hkv; a.n_ctx = context_size;
@@ -946,7 +940,8 @@ extern "C" int minf_sparse_attention_fwd(
     const int32_t* head_mode, const int32_t* head_param,
     const void* plan, const int32_t* vertical_indexes, int cap_v, int cap_s,
     int32_t* status, void* stream) {
-    return minf_sparse_attention_fwd_window(q, k, v, o, nullptr, q_strides, k_strides, v_strides, o_strides,
+    if (!o) return fail(MINF_E_ARG, "null pointer argument");
+    return minf_sparse_attention_fwd_window(q, k, v, o, nullptr, nullptr, nullptr, q_strides, k_strides, v_strides, o_strides,
                                             batch, hq, hkv, context_size, context_size, 0, context_size, 0,
                                             head_dim, sm_scale, head_mode, head_param, plan, vertical_indexes,
                                             cap_v, cap_s, status, stream);

@@ -118,7 +118,7 @@ def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx
     lse = torch.empty((B, H, n_q), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
-            _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse),
+            _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse), None, None,
             _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
             B, H, k.shape[1], n_ctx, n_q, q_pos0, n_kv, kv_pos0, D, float(sm_scale or D ** -0.5),
             _cabi.ptr(head_mode), _cabi.ptr(head_param), _cabi.ptr(plan), _cabi.ptr(v_idx),

@@ -59,7 +59,7 @@ def sparse_attention_forward(query, key, value, plan: SparsePlan | None, head_mo
         lse = torch.empty((B, H, N), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
-                _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse),
+                _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse), None, None,
                 _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
                 B, H, Hkv, N, N, 0, N, 0, D, float(sm_scale),
                 _cabi.ptr(head_mode), _cabi.ptr(head_param),

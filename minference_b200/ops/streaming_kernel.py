@@ -61,7 +61,7 @@ def tri_shape_kernel(q, k, v, config):
     status = _cabi.new_status(dev)
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
-            _cabi.ptr(qw), _cabi.ptr(kk), _cabi.ptr(vv), _cabi.ptr(out), None,
+            _cabi.ptr(qw), _cabi.ptr(kk), _cabi.ptr(vv), _cabi.ptr(out), None, None, None,
             _cabi.strides3(qw), _cabi.strides3(kk), _cabi.strides3(vv), _cabi.strides3(out),
             B, H, kk.shape[1], N, N - q0, q0, N, 0, D, float(D ** -0.5),
             _cabi.ptr(mode), _cabi.ptr(param), None, None, 0, 1, _cabi.ptr(status), _cabi.stream_ptr(dev)))
