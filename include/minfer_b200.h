@@ -47,6 +47,15 @@ const char* minf_version(void);
 const char* minf_last_error(void);
 
 /*
+ * Self-test of the bounded device wait: launches one CTA that waits on a barrier nothing arrives on.
+ * After `limit_us` microseconds (1 .. 1000000) the wait is abandoned and the kernel returns through its
+ * normal exit with bit 0 of status[MINF_ST_ERROR] set; the context stays usable.  Every wait inside the
+ * attention and estimator kernels takes the same path (with a limit of two seconds).  No counterpart
+ * in the reference.
+ */
+int minf_selftest_bounded_wait(int limit_us, int32_t* status, void* stream);
+
+/*
  * Reference-format index conversion.  Replaces
  *   minference.cuda.convert_vertical_slash_indexes (csrc/kernels.cpp:7-17,
  *   csrc/vertical_slash_index.cu:127-167, kernel :27-99).
@@ -153,29 +162,39 @@ int minf_vs_estimate(
     void* scratch, int32_t* status, void* stream);
 
 /*
- * The three stages of minf_vs_estimate as separate calls, for callers that hold only part of
- * the keys (sequence sharding): statistics pass over the local keys, exchange of the per-chunk
- * statistics, score pass, reduction of the score arrays over the ranks, selection.
+ * The stages of minf_vs_estimate as separate calls, for callers that hold only part of the keys
+ * (sequence sharding): statistics pass over the local keys, exchange of the per-block statistics,
+ * combination, score pass, reduction of the score arrays over the ranks, selection.
  *   q_last   the last min(64, context_size) queries of every head, [batch, hq, last_q, 128]
  *   k        the n_k local keys at positions [col_base, col_base + n_k) (col_base % 128 == 0)
- *   stats    float2 [batch*hq][64][chunks_total]; this call owns chunks
- *            [chunk_offset, chunk_offset + minf_vs_scores_chunks(batch, hq, hkv, n_k)).
- *            Pass 1 writes (row max, row sum) per chunk; pass 2 reads all chunks_total entries.
+ *   stats    float2 [batch*hq][64][blocks_total]: (row max, row sum) of the softmax per block of
+ *            2048 keys, blocks counted from col_base.  Pass 1 writes the
+ *            minf_vs_scores_blocks(n_k) entries that start at block_offset.  The caller lays the
+ *            blocks of the whole sequence out in ascending key order (all-gather, then reorder).
+ *   row_stats float2 [batch*hq][64]: written by minf_vs_scores_combine from all blocks_total
+ *            entries of a row, read by pass 2.
  *   vertical_scores / slash_scores   fp32 [batch, hq, context_size], zeroed by the caller before
- *            pass 2 (slash is indexed by diagonal offset and accumulated with atomics).
+ *            pass 2 (slash is indexed by diagonal offset; entries whose keys span two calls are
+ *            accumulated with atomics, every other entry is stored).
+ * When every chunk starts at a multiple of 2048 keys the scores, and with them the selected
+ * index lists, are bit-identical however the sequence is split over calls or ranks.
  * No counterpart in the reference beyond minference_forward.py:599-614.
  */
-int minf_vs_scores_chunks(int batch, int hq, int hkv, int n_k);
+int minf_vs_scores_blocks(int n_k);
 int minf_vs_scores_pass(
     int pass, const void* q_last, const void* k,
     const int64_t q_strides[3], const int64_t k_strides[3],
     int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim,
-    void* stats, int chunk_offset, int chunks_total, float* vertical_scores, float* slash_scores,
+    void* stats, int block_offset, int blocks_total, const void* row_stats,
+    float* vertical_scores, float* slash_scores,
     int32_t* status, void* stream);
+int minf_vs_scores_combine(const void* stats, int batch, int hq, int blocks_total, void* row_stats, void* stream);
+/* `scratch` holds minf_vs_select_scratch_bytes() bytes (histograms and per-segment counts). */
+size_t minf_vs_select_scratch_bytes(int batch, int hq, int context_size);
 int minf_vs_select(
     const float* vertical_scores, const float* slash_scores, int batch, int hq, int context_size,
     const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
-    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* stream);
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* scratch, void* stream);
 
 /*
  * minf_vs_estimate for callers that cannot provide scratch memory and must not trigger an

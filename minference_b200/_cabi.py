@@ -27,6 +27,7 @@ _I64x3 = POINTER(c_int64)
 SIGNATURES = {
     "minf_version": (c_char_p, []),
     "minf_last_error": (c_char_p, []),
+    "minf_selftest_bounded_wait": (c_int, [c_int, c_void_p, c_void_p]),
     "minf_convert_vertical_slash_indexes": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p] * 4 + [c_void_p, c_void_p]),
     "minf_plan_bytes": (c_size_t, [c_int] * 5),
     "minf_vs_build_plan": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p, c_void_p, c_void_p]),
@@ -40,11 +41,13 @@ SIGNATURES = {
     "minf_vs_estimate_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_estimate": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
                          [c_int, c_int] + [c_void_p] * 6 + [c_void_p, c_void_p, c_void_p]),
-    "minf_vs_scores_chunks": (c_int, [c_int] * 4),
+    "minf_vs_scores_blocks": (c_int, [c_int]),
     "minf_vs_scores_pass": (c_int, [c_int, c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 7 +
-                            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+                            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "minf_vs_scores_combine": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "minf_vs_select_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_select": (c_int, [c_void_p, c_void_p] + [c_int] * 3 + [c_void_p, c_void_p, c_int, c_int] +
-                       [c_void_p] * 4 + [c_void_p]),
+                       [c_void_p] * 4 + [c_void_p, c_void_p]),
     "minf_vs_estimate_static_scratch_limit": (c_size_t, []),
     "minf_vs_estimate_static": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
                                 [c_int, c_int] + [c_void_p] * 4 + [c_void_p, c_void_p]),

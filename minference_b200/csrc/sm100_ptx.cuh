@@ -67,19 +67,22 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Returns false when the wait was abandoned (limit hit, or another thread of the CTA
 // already gave up).  `abort_flag` lives in shared memory.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
     if (mbar_test(bar, parity)) return true;       // cheap probe first: most waits find the phase complete
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_for(bar, parity, abort_flag, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------- TMA (tile mode, one destination CTA)

@@ -156,17 +156,14 @@ __device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigne
 
 // One softmax step of one query row: S (fp32, NCH*32 columns at t_s) -> P (bf16 pairs written
 // back over the first NCH*16 columns).  The whole row is held in registers, so TMEM is read
-// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.  A 32-key chunk that no row of
-// the warp can see (the other row block's half of an isolated diagonal, keys past the causal
-// limit) is neither loaded nor exponentiated: its P is written as zeros.
-template <int NCH>
+// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.  SKIP: a 64-key half that no row
+// of the warp can see (the other row block's half of an isolated diagonal, keys past the causal
+// limit; live0 / live1 are warp-uniform) is not exponentiated: its P is written as zeros.
+template <int NCH, bool SKIP>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,
-                                            uint32_t bar_half0, uint32_t bar_half1) {
-    // bit c set <=> some row of this warp sees a key of chunk c (TMEM loads are warp-collective)
-    uint32_t live = ((uint32_t)m0 != 0u ? 1u : 0u) | ((uint32_t)(m0 >> 32) != 0u ? 2u : 0u);
-    if (NCH == 4) live |= ((uint32_t)m1 != 0u ? 4u : 0u) | ((uint32_t)(m1 >> 32) != 0u ? 8u : 0u);
-    live = __reduce_or_sync(0xffffffffu, live);
+                                            uint32_t bar_half0, uint32_t bar_half1, bool live0, bool live1) {
+    auto chunk_live = [&](int c) { return !SKIP || (c < NCH / 2 ? live0 : live1); };   // the halves P is published in
     // The row maximum of a chunk is taken while the next chunk's load is in flight.
     uint32_t sr[NCH][32];
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -175,7 +172,7 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
     for (int c = 0; c < NCH; ++c) {
         tmem_wait_ld();
         if (c + 1 < NCH) tmem_ld32(t_s + 32 * (c + 1), sr[c + 1]);
-        if ((live >> c) & 1u) {
+        if (chunk_live(c)) {
             const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
             if (cm != 0xffffffffu) {
 #pragma unroll
@@ -215,7 +212,7 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         uint32_t pk[16];
-        if ((live >> c) & 1u) {
+        if (chunk_live(c)) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
                 float x0, x1;
@@ -659,6 +656,13 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!ok) break;
                 const int4 nxt = read_step(j + 1);
                 const bool nxt_live = nxt.x != kEndStep;
+                // A slot that sits out this step has a free S: its next QK^T goes first, so that its
+                // softmax runs while this step's P is still being made (steps of scattered diagonals
+                // touch one slot each, alternating).
+                const int early = nxt_live ? (nxt.w & ~cur.w) : 0;
+#pragma unroll
+                for (int s = 0; s < 2; ++s)
+                    if ((early >> s) & 1) issue_s(j + 1, s, nxt.z);
                 ok = wait(&ctl->v_full[kv], kv_par);
                 if (!ok) break;
 #pragma unroll
@@ -673,9 +677,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         tc_fence_after();
                         issue_pv_half(j, kv, s, cur.z, 1);
                     }
-                    if (nxt_live && ((nxt.w >> s) & 1)) {
-                        issue_s(j + 1, s, nxt.z);
-                    }
+                    if (nxt_live && ((nxt.w & ~early) >> s) & 1) issue_s(j + 1, s, nxt.z);
                 }
                 if (!ok) break;
                 if (elect_one()) {
@@ -743,10 +745,16 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             ok = mbar_wait(bar(&ctl->s_full[slot]), n & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            if (width == 128)
-                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
-            else
-                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
+            // which halves of the step's keys can some row of this warp see?  (warp-uniform)
+            if (width == 128) {
+                const bool live0 = __any_sync(0xffffffffu, m0 != 0ull), live1 = __any_sync(0xffffffffu, m1 != 0ull);
+                if (live0 && live1)
+                    softmax_row<4, false>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), true, true);
+                else
+                    softmax_row<4, true>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), live0, live1);
+            } else {
+                softmax_row<2, false>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), true, true);
+            }
             ++n;
         }
 

@@ -15,10 +15,13 @@
 //     none of the ranges; since both lists are sorted this is a forward scan, done 32
 //     columns per step with ballots.
 //
-// Two output formats from the same walk:
-//   REF  -- the reference's dense tables (block_count/block_offset/column_count/column_index),
-//           bit-exact including zero tails;
-//   PLAN -- merged [start,end) ranges + a bit mask over the vertical list (plan_layout.h).
+// Two kernels share that walk:
+//   vs_convert_kernel -- the reference's dense tables (block_count/block_offset/column_count/
+//           column_index), bit-exact including zero tails; one warp per row block scans the list.
+//   vs_plan_kernel -- merged [start,end) ranges + a bit mask over the vertical list
+//           (plan_layout.h).  The gaps of the slash list do not depend on the row block, so a
+//           CTA compacts the positions whose gap exceeds 64 once and each of its 32 row blocks
+//           walks only those; the bit mask is built in shared memory, two words per step.
 #include <climits>
 
 #include "common.h"
@@ -27,7 +30,7 @@
 namespace minf {
 
 constexpr int kConvertWarps = 8;
-constexpr int kMaxBitWordsPerLane = 8;  // vertical lists up to 8192 entries in PLAN mode
+constexpr int kPlanRowsPerWarp = 4;    // a plan CTA covers 32 row blocks of one head
 
 struct ConvertArgs {
     const int32_t* seqlens;
@@ -37,18 +40,27 @@ struct ConvertArgs {
     const int32_t* nnz_s_per_head;
     int heads, rows, cap_v, cap_s;
     int rb_base;                      // first row block covered (0 for a whole sequence)
-    // REF outputs
+    // reference-format outputs
     int32_t* block_count;
     int32_t* block_offset;
     int32_t* column_count;
     int32_t* column_index;
-    // PLAN output
+    // plan output
     unsigned char* plan;
     PlanLayout layout;
     int32_t* status;
 };
 
-template <bool REF>
+// first slash entry below end_m (list is descending): lower bound, uniform across lanes
+__device__ __forceinline__ int first_slash_below(const int32_t* s_list, int nnz_s, int end_m) {
+    int lo = 0, hi = nnz_s;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s_list[mid] >= end_m) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
 __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const ConvertArgs a) {
     extern __shared__ int32_t lists[];
     int32_t* s_list = lists;
@@ -57,77 +69,38 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
     const int b = blockIdx.z, h = blockIdx.y;
     const int bh = b * a.heads + h;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (a.nnz_s_per_head && a.nnz_s_per_head[bh] < 0) return;   // head owned by another pattern
-    const int nnz_s = a.nnz_s_per_head ? min(a.nnz_s_per_head[bh], a.cap_s) : a.cap_s;
-    const int nnz_v = a.nnz_v_per_head ? min(a.nnz_v_per_head[bh], a.cap_v) : a.cap_v;
+    const int nnz_s = a.cap_s, nnz_v = a.cap_v;
 
     for (int i = threadIdx.x; i < nnz_s; i += blockDim.x) s_list[i] = a.s_idx[(size_t)bh * a.cap_s + i];
     for (int i = threadIdx.x; i < nnz_v; i += blockDim.x) v_list[i] = a.v_idx[(size_t)bh * a.cap_v + i];
     __syncthreads();
 
-    const int m = blockIdx.x * kConvertWarps + warp;          // row block inside the output
+    const int m = blockIdx.x * kConvertWarps + warp;          // row block
     if (m >= a.rows) return;
     const int seqlen = a.seqlens[b];
-    const int start_m = (a.rb_base + m) * 64, end_m = start_m + 64;   // its rows in the sequence
+    const int start_m = m * 64, end_m = start_m + 64;
     const size_t row = (size_t)bh * a.rows + m;
+    int32_t* bo = a.block_offset + row * a.cap_s;
+    int32_t* ci = a.column_index + row * a.cap_v;
 
-    int32_t* bo = nullptr;
-    int32_t* ci = nullptr;
-    int2* rng = nullptr;
-    if (REF) {
-        bo = a.block_offset + row * a.cap_s;
-        ci = a.column_index + row * a.cap_v;
-    } else {
-        rng = reinterpret_cast<int2*>(a.plan + (size_t)bh * a.layout.head_bytes + a.layout.rng_off) +
-              plan_rng_offset(a.layout, m);
-    }
-
-    int nblk = 0, ncol = 0, nrng = 0, vp = 0;
-    uint32_t bits[kMaxBitWordsPerLane];
-#pragma unroll
-    for (int i = 0; i < kMaxBitWordsPerLane; ++i) bits[i] = 0u;
-
-    // first slash entry below end_m (list is descending): lower bound, uniform across lanes
+    int nblk = 0, ncol = 0, vp = 0;
     int i0 = nnz_s;
     if (start_m < seqlen) {
-        int lo = 0, hi = nnz_s;
-        while (lo < hi) {
-            int mid = (lo + hi) >> 1;
-            if (s_list[mid] >= end_m) lo = mid + 1; else hi = mid;
-        }
-        i0 = lo;
+        i0 = first_slash_below(s_list, nnz_s, end_m);
         if (i0 == nnz_s && lane == 0) atomicAdd(a.status + MINF_ST_NO_SLASH, 1);
     }
 
     if (i0 < nnz_s) {
-        // close range [rs, re): emit its tiles / record it, then advance through the verticals
+        // close range [rs, re): emit its tiles, then advance through the verticals
         auto close_range = [&](int rs, int re) {
-            if (REF) {
-                for (int t = rs + 64 * lane; t < re; t += 64 * 32) bo[nblk + ((t - rs) >> 6)] = t;
-                nblk += (re - rs) >> 6;
-            } else {
-                if (lane == 0) rng[nrng] = make_int2(rs, re);
-                ++nrng;
-            }
+            for (int t = rs + 64 * lane; t < re; t += 64 * 32) bo[nblk + ((t - rs) >> 6)] = t;
+            nblk += (re - rs) >> 6;
             for (;;) {
                 const int i = vp + lane;
                 const int val = i < nnz_v ? v_list[i] : INT_MAX;
                 const int n_below = __popc(__ballot_sync(0xffffffffu, val < rs));
-                if (REF) {
-                    if (lane < n_below) ci[ncol + lane] = val;
-                    ncol += n_below;
-                } else if (n_below) {
-                    const int lo_bit = vp, hi_bit = vp + n_below;
-#pragma unroll
-                    for (int w = 0; w < kMaxBitWordsPerLane; ++w) {
-                        const int base = 32 * (lane + 32 * w);
-                        const int lo = max(lo_bit, base), hi = min(hi_bit, base + 32);
-                        if (lo < hi) {
-                            const int n = hi - lo;
-                            bits[w] |= (n == 32 ? 0xffffffffu : ((1u << n) - 1u)) << (lo - base);
-                        }
-                    }
-                }
+                if (lane < n_below) ci[ncol + lane] = val;
+                ncol += n_below;
                 const int n_inside = __popc(__ballot_sync(0xffffffffu, val < re));
                 vp += n_inside;
                 if (n_inside < 32) break;
@@ -160,22 +133,127 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
         close_range(e_first - 64, e_first + ((carry - e_first + 63) & ~63));
     }
 
-    if (REF) {
-        if (lane == 0) {
-            a.block_count[row] = nblk;
-            a.column_count[row] = ncol;
-        }
-        for (int j = nblk + lane; j < a.cap_s; j += 32) bo[j] = 0;
-        for (int j = ncol + lane; j < a.cap_v; j += 32) ci[j] = 0;
-    } else {
-        unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
-        if (lane == 0) reinterpret_cast<int32_t*>(slot)[m] = nrng;
-        uint32_t* wb = reinterpret_cast<uint32_t*>(slot + a.layout.bits_off) + (size_t)m * a.layout.words_v;
+    if (lane == 0) {
+        a.block_count[row] = nblk;
+        a.column_count[row] = ncol;
+    }
+    for (int j = nblk + lane; j < a.cap_s; j += 32) bo[j] = 0;
+    for (int j = ncol + lane; j < a.cap_v; j += 32) ci[j] = 0;
+}
+
+__global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const ConvertArgs a) {
+    extern __shared__ int32_t lists[];
+    int32_t* s_list = lists;
+    int32_t* v_list = lists + a.cap_s;
+    int32_t* cand = v_list + a.cap_v;                      // positions j with s[j-1] - s[j] > 64, ascending
+    uint32_t* wbits = reinterpret_cast<uint32_t*>(cand + a.cap_s);   // [warp][words_v]
+    __shared__ int warp_count[kConvertWarps];
+    __shared__ int sh_ncand;
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int bh = b * a.heads + h;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (a.nnz_s_per_head && a.nnz_s_per_head[bh] < 0) return;   // head owned by another pattern
+    const int nnz_s = a.nnz_s_per_head ? min(a.nnz_s_per_head[bh], a.cap_s) : a.cap_s;
+    const int nnz_v = a.nnz_v_per_head ? min(max(a.nnz_v_per_head[bh], 0), a.cap_v) : a.cap_v;
+    const int words_v = a.layout.words_v;
+
+    for (int i = threadIdx.x; i < nnz_s; i += blockDim.x) s_list[i] = a.s_idx[(size_t)bh * a.cap_s + i];
+    for (int i = threadIdx.x; i < nnz_v; i += blockDim.x) v_list[i] = a.v_idx[(size_t)bh * a.cap_v + i];
+    if (threadIdx.x == 0) sh_ncand = 0;
+    __syncthreads();
+    // ordered compaction of the gap positions, one block-wide round per 256 entries
+    for (int base = 1; base < nnz_s; base += kConvertWarps * 32) {
+        const int j = base + threadIdx.x;
+        const bool is_gap = j < nnz_s && s_list[j - 1] - s_list[j] > 64;
+        const unsigned bal = __ballot_sync(0xffffffffu, is_gap);
+        if (lane == 0) warp_count[warp] = __popc(bal);
+        __syncthreads();
+        int dst = sh_ncand + __popc(bal & ((1u << lane) - 1u));
+        int total = 0;
 #pragma unroll
-        for (int w = 0; w < kMaxBitWordsPerLane; ++w) {
-            const int idx = lane + 32 * w;
-            if (idx < a.layout.words_v) wb[idx] = bits[w];
+        for (int w = 0; w < kConvertWarps; ++w) {
+            if (w < warp) dst += warp_count[w];
+            total += warp_count[w];
         }
+        if (is_gap) cand[dst] = j;
+        __syncthreads();
+        if (threadIdx.x == 0) sh_ncand += total;
+    }
+    __syncthreads();
+    const int n_cand = sh_ncand;
+    uint32_t* wb = wbits + warp * words_v;
+    unsigned char* slot = a.plan + (size_t)bh * a.layout.head_bytes;
+
+    for (int rr = 0; rr < kPlanRowsPerWarp; ++rr) {
+        const int m = (blockIdx.x * kPlanRowsPerWarp + rr) * kConvertWarps + warp;    // row block inside the output
+        if (m >= a.rows) break;
+        const int seqlen = a.seqlens[b];
+        const int start_m = (a.rb_base + m) * 64, end_m = start_m + 64;   // its rows in the sequence
+        int2* rng = reinterpret_cast<int2*>(slot + a.layout.rng_off) + plan_rng_offset(a.layout, m);
+        for (int w = lane; w < words_v; w += 32) wb[w] = 0u;
+        __syncwarp();
+
+        int nrng = 0, vp = 0;
+        int i0 = nnz_s;
+        if (start_m < seqlen) {
+            i0 = first_slash_below(s_list, nnz_s, end_m);
+            if (i0 == nnz_s && lane == 0) atomicAdd(a.status + MINF_ST_NO_SLASH, 1);
+        }
+        if (i0 < nnz_s) {
+            // close range [rs, re): record it, then advance through the verticals; the columns below
+            // rs that no earlier range covered are gathered: their bits span at most two words
+            auto close_range = [&](int rs, int re) {
+                if (lane == 0) rng[nrng] = make_int2(rs, re);
+                ++nrng;
+                for (;;) {
+                    const int i = vp + lane;
+                    const int val = i < nnz_v ? v_list[i] : INT_MAX;
+                    const int n_below = __popc(__ballot_sync(0xffffffffu, val < rs));
+                    if (n_below && lane == 0) {
+                        const int lo = vp, hi = vp + n_below;
+                        const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
+                        const int top = min(hi - 32 * w0, 32);
+                        wb[w0] |= (top == 32 ? 0xffffffffu : ((1u << top) - 1u)) & ~((1u << (lo & 31)) - 1u);
+                        if (w1 != w0) wb[w1] |= (hi - 32 * w1 == 32) ? 0xffffffffu : ((1u << (hi - 32 * w1)) - 1u);
+                    }
+                    const int n_inside = __popc(__ballot_sync(0xffffffffu, val < re));
+                    vp += n_inside;
+                    if (n_inside < 32) break;
+                }
+            };
+            // first gap position after i0
+            int lo = 0, hi = n_cand;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (cand[mid] <= i0) lo = mid + 1; else hi = mid;
+            }
+            int e_first = max(end_m - s_list[i0], 64);
+            for (int base = lo; base < n_cand; base += 32) {
+                const bool valid = base + lane < n_cand;
+                const int j = valid ? cand[base + lane] : 1;
+                const int e = max(end_m - s_list[j], 64), prev = max(end_m - s_list[j - 1], 64);
+                unsigned open = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
+                while (open) {
+                    const int l = __ffs(open) - 1;
+                    open &= open - 1;
+                    const int ej = __shfl_sync(0xffffffffu, e, l);
+                    const int pj = __shfl_sync(0xffffffffu, prev, l);
+                    const int re = e_first + ((pj - e_first + 63) & ~63);
+                    if (ej > re + 64) {
+                        close_range(e_first - 64, re);
+                        e_first = ej;
+                    }
+                }
+            }
+            const int e_last = max(end_m - s_list[nnz_s - 1], 64);
+            close_range(e_first - 64, e_first + ((e_last - e_first + 63) & ~63));
+        }
+        __syncwarp();
+        if (lane == 0) reinterpret_cast<int32_t*>(slot)[m] = nrng;
+        uint32_t* out = reinterpret_cast<uint32_t*>(slot + a.layout.bits_off) + (size_t)m * words_v;
+        for (int w = lane; w < words_v; w += 32) out[w] = wb[w];
+        __syncwarp();
     }
 }
 
@@ -199,18 +277,24 @@ __global__ void plan_count_tiles_kernel(const unsigned char* plan, PlanLayout L,
     if ((threadIdx.x & 31) == 0 && tiles) atomicAdd(out, tiles);
 }
 
-static int launch_convert(bool ref, const ConvertArgs& a, int batch, cudaStream_t st) {
+static int launch_convert(const ConvertArgs& a, int batch, cudaStream_t st) {
     const size_t smem = (size_t)(a.cap_s + a.cap_v) * sizeof(int32_t);
     if (smem > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "index lists too long for shared memory (%zu bytes)", smem);
     dim3 grid((a.rows + kConvertWarps - 1) / kConvertWarps, a.heads, batch);
-    if (ref) {
-        MINF_CUDA_OK(cudaFuncSetAttribute(vs_convert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        vs_convert_kernel<true><<<grid, kConvertWarps * 32, smem, st>>>(a);
-    } else {
-        MINF_CUDA_OK(cudaFuncSetAttribute(vs_convert_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        vs_convert_kernel<false><<<grid, kConvertWarps * 32, smem, st>>>(a);
-    }
+    MINF_CUDA_OK(cudaFuncSetAttribute(vs_convert_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    vs_convert_kernel<<<grid, kConvertWarps * 32, smem, st>>>(a);
     MINF_LAUNCH_OK("vs_convert_kernel");
+    return MINF_OK;
+}
+
+static int launch_plan(const ConvertArgs& a, int batch, cudaStream_t st) {
+    const size_t smem = ((size_t)2 * a.cap_s + a.cap_v + (size_t)kConvertWarps * a.layout.words_v) * sizeof(int32_t);
+    if (smem > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "index lists too long for shared memory (%zu bytes)", smem);
+    const int per_cta = kConvertWarps * kPlanRowsPerWarp;
+    dim3 grid((a.rows + per_cta - 1) / per_cta, a.heads, batch);
+    MINF_CUDA_OK(cudaFuncSetAttribute(vs_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    vs_plan_kernel<<<grid, kConvertWarps * 32, smem, st>>>(a);
+    MINF_LAUNCH_OK("vs_plan_kernel");
     return MINF_OK;
 }
 
@@ -235,7 +319,7 @@ extern "C" int minf_convert_vertical_slash_indexes(
     a.block_count = block_count; a.block_offset = block_offset;
     a.column_count = column_count; a.column_index = column_index;
     a.status = status;
-    return launch_convert(true, a, batch, static_cast<cudaStream_t>(stream));
+    return launch_convert(a, batch, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t minf_plan_bytes(int batch, int heads, int context_size, int cap_v, int cap_s) {
@@ -258,8 +342,6 @@ extern "C" int minf_vs_build_plan_window(
     if (batch < 1 || heads < 1 || n_q < 1 || q_pos0 < 0 || (q_pos0 % 64) || cap_v < 1 || cap_s < 1 || heads > 65535 || batch > 65535)
         return fail(MINF_E_ARG, "bad sizes: batch=%d heads=%d q_pos0=%d n_q=%d cap_v=%d cap_s=%d", batch, heads,
                     q_pos0, n_q, cap_v, cap_s);
-    if (cap_v > 32 * 32 * kMaxBitWordsPerLane)
-        return fail(MINF_E_UNSUPPORTED, "cap_v=%d exceeds %d", cap_v, 32 * 32 * kMaxBitWordsPerLane);
     ConvertArgs a{};
     a.seqlens = seqlens; a.v_idx = vertical_indexes; a.s_idx = slash_indexes;
     a.nnz_v_per_head = nnz_v_per_head; a.nnz_s_per_head = nnz_s_per_head;
@@ -268,7 +350,7 @@ extern "C" int minf_vs_build_plan_window(
     a.plan = static_cast<unsigned char*>(plan);
     a.layout = make_plan_layout_window(a.rb_base, a.rows, cap_v, cap_s);
     a.status = status;
-    return launch_convert(false, a, batch, static_cast<cudaStream_t>(stream));
+    return launch_plan(a, batch, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int minf_vs_build_plan(

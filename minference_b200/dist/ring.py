@@ -9,7 +9,8 @@ same global index lists and builds the plans of its own query chunks.  The atten
 is a ring: in step t a rank holds the K/V shard of rank r-t, attends its two query chunks to
 the shard's two key chunks (pairs that lie entirely in the future are skipped) and passes the
 shard on while it computes.  Partial results of different key chunks are merged through the
-per-row log-sum-exp the kernel writes.
+per-row log-sum-exp: the kernel carries an fp32 accumulator from one key chunk to the next and
+rounds the output once, with the last chunk.
 
 Everything that touches the GPU goes through the C ABI; the orchestration (chunk schedule,
 communication, merge) is plain torch so that it can be exercised on CPU ranks (gloo) with a
@@ -108,18 +109,26 @@ def count_tiles_window(plan, batch: int, heads: int, q_pos0: int, n_q: int, cap_
 
 
 def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx, cap_s: int, status, sm_scale=None,
-                     head_mode=None, head_param=None, cap_v: int | None = None):
+                     head_mode=None, head_param=None, cap_v: int | None = None, carry=None, out=None):
     """One (query chunk, key chunk) pair through ``minf_sparse_attention_fwd_window``.
-    ``head_mode`` / ``head_param`` select per head between the plan and the A-shape mask."""
+    ``head_mode`` / ``head_param`` select per head between the plan and the A-shape mask.
+
+    Without ``carry`` the call returns the normalised partial output and its base-2 log-sum-exp.
+    With ``carry = (o_acc fp32 [B,H,n_q,D], lse_acc fp32 [B,H,n_q])`` the kernel folds this key chunk
+    into the carried result itself (in fp32, see the header) and ``out`` -- given for the last key
+    chunk of a query chunk -- receives the merged result rounded to the input dtype once."""
     B, H, n_q, D = q.shape
     n_kv = k.shape[2]
     dev = q.device
-    out = torch.empty((B, H, n_q, D), dtype=q.dtype, device=dev)
-    lse = torch.empty((B, H, n_q), dtype=torch.float32, device=dev)
+    lse = None
+    if carry is None:
+        out = torch.empty((B, H, n_q, D), dtype=q.dtype, device=dev) if out is None else out
+        lse = torch.empty((B, H, n_q), dtype=torch.float32, device=dev)
+    o_acc, lse_acc = carry if carry is not None else (None, None)
     with torch.cuda.device(dev):
         _cabi.check(_cabi.lib().minf_sparse_attention_fwd_window(
-            _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse), None, None,
-            _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out),
+            _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(out), _cabi.ptr(lse), _cabi.ptr(o_acc), _cabi.ptr(lse_acc),
+            _cabi.strides3(q), _cabi.strides3(k), _cabi.strides3(v), _cabi.strides3(out) if out is not None else None,
             B, H, k.shape[1], n_ctx, n_q, q_pos0, n_kv, kv_pos0, D, float(sm_scale or D ** -0.5),
             _cabi.ptr(head_mode), _cabi.ptr(head_param), _cabi.ptr(plan), _cabi.ptr(v_idx),
             cap_v if cap_v is not None else (v_idx.shape[2] if v_idx is not None else 0), cap_s,
@@ -127,11 +136,35 @@ def attention_window(q, k, v, n_ctx: int, q_pos0: int, kv_pos0: int, plan, v_idx
     return out, lse
 
 
+def _ordered_blocks(gathered: torch.Tensor, world: int, bl: int) -> torch.Tensor:
+    """``[world, R, 64, 2*bl, 2]`` (every rank's two chunks, rank-major) -> ``[R, 64, 2*world*bl, 2]`` with the
+    statistics blocks in ascending key order: chunk r is rank r's first, chunk 2*world-1-r its second."""
+    g = gathered.view(world, gathered.shape[1], 64, 2, bl, 2)
+    first = g[:, :, :, 0].permute(1, 2, 0, 3, 4)
+    second = g[:, :, :, 1].flip(0).permute(1, 2, 0, 3, 4)
+    return torch.cat((first, second), dim=2).reshape(gathered.shape[1], 64, 2 * world * bl, 2).contiguous()
+
+
+def slash_window(n_ctx: int, chunk: int, c: int):
+    """Diagonal offsets the keys of chunk ``chunk`` can contribute to: ``[lo, hi)``.  A diagonal is 64 queries
+    long, so neighbouring chunks share 63 offsets."""
+    last_q = min(64, n_ctx)
+    lo = max(0, (n_ctx - last_q) - (chunk + 1) * c + 1)
+    hi = min(n_ctx, n_ctx - chunk * c)
+    return lo, hi
+
+
 def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_size, group=None,
                                  cap_v: int | None = None, cap_s: int | None = None):
     """Global index lists from sharded K: ``(v_idx, s_idx, nnz_v, nnz_s)``, identical on all ranks.
     The budgets are ints (every head) or int32 tensors ``[H]`` with -1 for heads that are not
-    vertical-slash (their lists are left unset and ``nnz`` is -1); tensors need ``cap_v`` / ``cap_s``."""
+    vertical-slash (their lists are left unset and ``nnz`` is -1); tensors need ``cap_v`` / ``cap_s``.
+
+    Exchanges: the last 64 queries (broadcast), the per-block softmax statistics (all-gather, a few MB),
+    and each rank's own part of the score arrays (one all-gather: vertical scores of its keys and the
+    diagonal offsets its keys reach).  Overlapping diagonal parts are added in chunk order, and the
+    statistics blocks are combined in key order, so the lists do not depend on the number of ranks
+    (for chunks that are multiples of 2048 tokens)."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     B, H, n_loc, D = q_loc.shape
     Hkv = k_loc.shape[1]
@@ -141,28 +174,45 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_
     # the last 64 queries live at the end of rank 0's second chunk
     q_last = q_loc[:, :, -64:, :].contiguous() if rank == 0 else torch.empty((B, H, 64, D), dtype=q_loc.dtype, device=dev)
     dist.broadcast(q_last, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
-    cl = L.minf_vs_scores_chunks(B, H, Hkv, c)
-    stats = torch.zeros((B * H, 64, 2 * cl, 2), dtype=torch.float32, device=dev)
-    stats[..., 0] = NEG_INF
+    bl = L.minf_vs_scores_blocks(c)
+    stats = torch.empty((B * H, 64, 2 * bl, 2), dtype=torch.float32, device=dev)
     status = _cabi.new_status(dev)
     chunks = owned_chunks(rank, world)
     k_parts = [k_loc[:, :, :c], k_loc[:, :, c:]]
 
-    def run(pass_, stats_t, offset_of, total, vertical, slash):
+    def run(pass_, stats_t, total, row_stats, vertical, slash):
         for i, (ci, kp) in enumerate(zip(chunks, k_parts)):
             with torch.cuda.device(dev):
                 _cabi.check(L.minf_vs_scores_pass(
                     pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
-                    B, H, Hkv, n_ctx, c, ci * c, D, _cabi.ptr(stats_t), offset_of(i), total,
+                    B, H, Hkv, n_ctx, c, ci * c, D, _cabi.ptr(stats_t), i * bl, total, _cabi.ptr(row_stats),
                     _cabi.ptr(vertical), _cabi.ptr(slash), _cabi.ptr(status), _cabi.stream_ptr(dev)))
 
-    run(1, stats, lambda i: i * cl, 2 * cl, None, None)
-    gathered = [torch.empty_like(stats) for _ in range(world)]
-    dist.all_gather(gathered, stats, group=group)
-    all_stats = torch.cat(gathered, dim=2).contiguous()           # [B*H, 64, world*2*cl, 2]
+    run(1, stats, 2 * bl, None, None, None)
+    gathered = torch.empty((world,) + tuple(stats.shape), dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(gathered, stats, group=group)
+    all_stats = _ordered_blocks(gathered, world, bl)            # [B*H, 64, 2*world*bl, 2], ascending key order
+    row_stats = torch.empty((B * H, 64, 2), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(L.minf_vs_scores_combine(_cabi.ptr(all_stats), B, H, all_stats.shape[2], _cabi.ptr(row_stats),
+                                             _cabi.stream_ptr(dev)))
     scores = torch.zeros((2, B, H, n_ctx), dtype=torch.float32, device=dev)
-    run(2, all_stats, lambda i: 0, all_stats.shape[2], scores[0], scores[1])
-    dist.all_reduce(scores, group=group)
+    run(2, None, 2 * world * bl, row_stats, scores[0], scores[1])
+    # every rank contributes the vertical scores of its own keys and the diagonal offsets those keys reach
+    wins = [slash_window(n_ctx, ci, c) for ci in chunks]
+    width = c + 64
+    pack = torch.zeros((B, H, 2, c + width), dtype=torch.float32, device=dev)
+    for i, (ci, (lo, hi)) in enumerate(zip(chunks, wins)):
+        pack[:, :, i, :c] = scores[0][:, :, ci * c:(ci + 1) * c]
+        pack[:, :, i, c:c + hi - lo] = scores[1][:, :, lo:hi]
+    everyone = torch.empty((world,) + tuple(pack.shape), dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(everyone, pack, group=group)
+    scores[1].zero_()
+    for chunk in range(2 * world):          # ascending chunk order: the 63 shared offsets are added in a fixed order
+        r, i = (chunk, 0) if chunk < world else (2 * world - 1 - chunk, 1)
+        lo, hi = slash_window(n_ctx, chunk, c)
+        scores[0][:, :, chunk * c:(chunk + 1) * c] = everyone[r, :, :, i, :c]
+        scores[1][:, :, lo:hi] += everyone[r, :, :, i, c:c + hi - lo]
     if torch.is_tensor(vertical_size):
         vs = vertical_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()
         ss = slash_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()
@@ -174,25 +224,31 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_
     s_idx = torch.empty((B, H, cap_s), dtype=torch.int32, device=dev)
     nnz_v = torch.empty((B * H,), dtype=torch.int32, device=dev)
     nnz_s = torch.empty((B * H,), dtype=torch.int32, device=dev)
+    scratch = torch.empty(L.minf_vs_select_scratch_bytes(B, H, n_ctx), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _cabi.check(L.minf_vs_select(_cabi.ptr(scores[0]), _cabi.ptr(scores[1]), B, H, n_ctx, _cabi.ptr(vs), _cabi.ptr(ss),
                                      cap_v, cap_s, _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
-                                     _cabi.stream_ptr(dev)))
+                                     _cabi.ptr(scratch), _cabi.stream_ptr(dev)))
     _cabi.raise_on_status(status, "ring_vertical_slash_estimate")
     return v_idx, s_idx, nnz_v, nnz_s
 
 
 # ------------------------------------------------------------------------------ the ring
 
-AttnFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor, int, int, int], tuple]
+AttnFn = Callable[..., tuple]
 
 
-def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None):
-    """Ring schedule, communication and merge.
+def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None, fused_merge: bool = False):
+    """Ring schedule and communication.
 
-    ``attn_fn(q_chunk, k_chunk, v_chunk, q_chunk_index, q_pos0, kv_pos0)`` must return the
-    normalised partial output and its base-2 log-sum-exp for the keys it was given.
-    Returns the local output ``[B,H,2C,D]`` in the dtype of ``q_loc``.
+    ``fused_merge=False``: ``attn_fn(q_chunk, k_chunk, v_chunk, q_chunk_index, q_pos0, kv_pos0)`` returns the
+    normalised partial output and its base-2 log-sum-exp for the keys it was given, and the partials
+    are merged here with torch ops (the CPU stand-ins of the tests work this way).
+    ``fused_merge=True``: ``attn_fn(..., carry, out)`` folds the key chunk into ``carry = (o_acc, lse_acc)``
+    itself and writes the merged rows to ``out`` when it is not ``None`` (the CUDA kernel does both
+    in its epilogue); ``out`` is passed with the last key chunk a query chunk sees.
+    Returns the local output ``[B,H,2C,D]`` in the dtype of ``q_loc``.  The K/V receive buffers,
+    the accumulators and the output are allocated once per call.
     """
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     c = chunk_size(n_ctx, world)
@@ -200,11 +256,16 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None)
     dev = q_loc.device
     q_chunks = owned_chunks(rank, world)
     q_parts = [q_loc[:, :, :c], q_loc[:, :, c:]]
-    acc_o = [torch.zeros((B, H, c, D), dtype=torch.float32, device=dev) for _ in range(2)]
-    acc_l = [torch.full((B, H, c), NEG_INF, dtype=torch.float32, device=dev) for _ in range(2)]
+    acc_o = torch.empty((2, B, H, c, D), dtype=torch.float32, device=dev)
+    if not fused_merge:
+        acc_o.zero_()
+    acc_l = torch.full((2, B, H, c), NEG_INF, dtype=torch.float32, device=dev)
+    out = torch.empty((B, H, 2 * c, D), dtype=q_loc.dtype, device=dev)
+    # how many key chunks each query chunk will see over the whole ring
+    pairs_left = [sum(1 for kc in range(2 * world) if pair_is_visible(qc, kc)) for qc in q_chunks]
 
-    kv = torch.stack((k_loc, v_loc)).contiguous()          # one message per step
-    nxt = torch.empty_like(kv)
+    kv = (k_loc, v_loc)                                   # the caller's tensors are sent as they are
+    bufs = [tuple(torch.empty_like(t) for t in kv) for _ in range(2 if world > 2 else 1)] if world > 1 else []
     send_to = (rank + 1) % world
     recv_from = (rank - 1) % world
     if group is not None:
@@ -213,8 +274,11 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None)
     for step in range(world):
         src = (rank - step) % world
         reqs = []
+        nxt = None
         if step + 1 < world:       # pass the shard on while this step computes
-            ops = [dist.P2POp(dist.isend, kv, send_to, group), dist.P2POp(dist.irecv, nxt, recv_from, group)]
+            nxt = bufs[step % len(bufs)]
+            ops = [dist.P2POp(dist.isend, kv[0], send_to, group), dist.P2POp(dist.isend, kv[1], send_to, group),
+                   dist.P2POp(dist.irecv, nxt[0], recv_from, group), dist.P2POp(dist.irecv, nxt[1], recv_from, group)]
             reqs = dist.batch_isend_irecv(ops)
         kv_chunks = owned_chunks(src, world)
         for qi, qc in enumerate(q_chunks):
@@ -223,13 +287,21 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None)
                     continue
                 k_part = kv[0][:, :, ki * c:(ki + 1) * c]
                 v_part = kv[1][:, :, ki * c:(ki + 1) * c]
-                o, lse = attn_fn(q_parts[qi], k_part, v_part, qi, qc * c, kc * c)
-                merge_partial(acc_o[qi], acc_l[qi], o, lse)
+                pairs_left[qi] -= 1
+                if fused_merge:
+                    attn_fn(q_parts[qi], k_part, v_part, qi, qc * c, kc * c, (acc_o[qi], acc_l[qi]),
+                            out[:, :, qi * c:(qi + 1) * c] if pairs_left[qi] == 0 else None)
+                else:
+                    o, lse = attn_fn(q_parts[qi], k_part, v_part, qi, qc * c, kc * c)
+                    merge_partial(acc_o[qi], acc_l[qi], o, lse)
         for r in reqs:
             r.wait()
-        if step + 1 < world:
-            kv, nxt = nxt, kv      # the next receive is ordered after this step's kernels by the stream
-    return torch.cat(acc_o, dim=2).to(q_loc.dtype)
+        if nxt is not None:
+            kv = nxt               # the next receive into the other buffer set is ordered after this step's kernels
+    if not fused_merge:
+        out[:, :, :c] = acc_o[0].to(q_loc.dtype)
+        out[:, :, c:] = acc_o[1].to(q_loc.dtype)
+    return out
 
 
 def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size: int = 1000, slash_size: int = 6096,
@@ -250,25 +322,33 @@ def ring_vertical_slash_attention(q_loc, k_loc, v_loc, n_ctx: int, vertical_size
     for qc in owned_chunks(rank, world):
         plans.append(build_plan_window(v_idx, s_idx, nnz_v, nnz_s, n_ctx, qc * c, c))
 
-    def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
+    def attn_fn(q, k, v, qi, q_pos0, kv_pos0, carry, out):
         plan, status = plans[qi]
         if stats is not None:      # CUDA-event timing of the attention launches (benchmarks)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        res = attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, s_idx.shape[2], status)
+        attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, s_idx.shape[2], status, carry=carry, out=out)
         if stats is not None:
             e1.record()
             stats.setdefault("attn_events", []).append((e0, e1))
-        return res
 
-    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
-    if stats is not None and stats.get("count_tiles"):
-        B, H = q_loc.shape[0], q_loc.shape[1]
-        stats["tiles"] = sum(count_tiles_window(plan, B, H, qc * c, c, v_idx.shape[2], s_idx.shape[2])
-                             for (plan, _), qc in zip(plans, owned_chunks(rank, world)))
+    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group, fused_merge=True)
+    if stats is not None:
+        stats["indices"] = indices
+        if stats.get("count_tiles"):
+            B, H = q_loc.shape[0], q_loc.shape[1]
+            stats["tiles"] = sum(count_tiles_window(plan, B, H, qc * c, c, v_idx.shape[2], s_idx.shape[2])
+                                 for (plan, _), qc in zip(plans, owned_chunks(rank, world)))
+            stats["issued"] = sum(issued_tiles(status) for _, status in plans)
     for plan, status in plans:
         _cabi.raise_on_status(status, "ring_vertical_slash_attention")
     return out
+
+
+def issued_tiles(status: torch.Tensor) -> int:
+    """64x64 tile equivalents the attention launches that shared ``status`` sent to the tensor pipe."""
+    st = status.tolist()
+    return (st[2] & 0xFFFFFFFF) | ((st[3] & 0xFFFFFFFF) << 32)
 
 
 def _pooled_blocks(x):
@@ -320,12 +400,12 @@ def ring_prefill_attention(q_loc, k_loc, v_loc, n_ctx: int, pattern, group=None,
                     _cabi.ptr(q_pool), _cabi.ptr(k_pool_all), B, H, k_loc.shape[1], n_ctx, qc * c, c, int(block_sparse_top_k),
                     _cabi.ptr(pattern.block_select), cap_v, cap_s, _cabi.ptr(plans[qi][0]), _cabi.stream_ptr(dev)))
 
-    def attn_fn(q, k, v, qi, q_pos0, kv_pos0):
+    def attn_fn(q, k, v, qi, q_pos0, kv_pos0, carry, out):
         plan, status = plans[qi]
-        return attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, cap_s, status,
-                                head_mode=pattern.head_mode, head_param=pattern.head_param, cap_v=cap_v)
+        attention_window(q, k, v, n_ctx, q_pos0, kv_pos0, plan, v_idx, cap_s, status,
+                         head_mode=pattern.head_mode, head_param=pattern.head_param, cap_v=cap_v, carry=carry, out=out)
 
-    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group)
+    out = ring_attention(q_loc, k_loc, v_loc, n_ctx, attn_fn, group, fused_merge=True)
     for _, status in plans:
         _cabi.raise_on_status(status, "ring_prefill_attention")
     return out

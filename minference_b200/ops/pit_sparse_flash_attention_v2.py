@@ -27,7 +27,7 @@ def build_vertical_slash_plan(v_idx: torch.Tensor, s_idx: torch.Tensor, context_
             _cabi.ptr(seqlens), _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
             B, H, context_size, cap_v, cap_s, _cabi.ptr(plan), _cabi.ptr(status), _cabi.stream_ptr(dev)))
     return SparsePlan(plan=plan, v_idx=v_idx, cap_v=cap_v, cap_s=cap_s, context_size=context_size,
-                      batch=B, heads=H, status=status)
+                      batch=B, heads=H, status=status, s_idx=s_idx)
 
 
 def vertical_slash_sparse_attention(

@@ -19,6 +19,7 @@ class SparsePlan:
     batch: int
     heads: int
     status: torch.Tensor
+    s_idx: torch.Tensor | None = None      # the slash lists the plan was built from (kept for checks)
 
     def count_tiles(self) -> int:
         """64x64 tiles the reference kernel would compute for this index set."""

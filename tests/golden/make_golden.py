@@ -1,6 +1,7 @@
 """Generate the golden fixtures in this folder from the reference itself.
 
-Run in a container that has the reference tree (default ``/root/reference``):
+Run where the reference tree (microsoft/MInference v0.1.6.0) is checked out: ``MINFERENCE_REFERENCE``
+points at it, or it sits in a directory named ``reference`` beside this repository:
 
     python oracle/build_ref.py --host
     python tests/golden/make_golden.py
@@ -15,6 +16,10 @@ What is executed is the reference's own code, not this repository's restatement:
   cannot be imported as a whole (it creates CUDA tensors at import time).  The call to
   ``vertical_slash_sparse_attention`` inside is replaced by a recorder of its index
   arguments.
+* ``estimator_bf16_*.npz`` -- the same function bodies executed on bf16 tensors (the dtype the
+  reference runs in on the GPU: bf16 GEMM output, bf16 division by sqrt(d), fp32 softmax), with
+  the score vectors it hands to ``torch.topk`` recorded beside the index lists, so that a test
+  can tell a wrong selection from a near-tie at the top-k boundary.
 * ``block_index_*.npz`` -- ``_build_block_index`` of
   ``minference/ops/block_sparse_flash_attention.py`` loaded by file path.
 
@@ -40,7 +45,9 @@ sys.path.insert(0, ROOT)
 
 from oracle import reference_math as R  # noqa: E402  (only for the ctypes loader of the reference host library)
 
-REFERENCE = os.environ.get("MINFERENCE_REFERENCE", "/root/reference")
+from oracle.build_ref import reference_tree  # noqa: E402
+
+REFERENCE = reference_tree()
 
 
 def index_case(seed: int, n: int, heads: int, nnz_v: int, nnz_s: int, style: str):
@@ -98,7 +105,22 @@ def make_index_fixtures(digests: dict):
                                        "tiles": int(outs[0].sum() + ((outs[2] + 63) // 64).sum())}
 
 
-def load_reference_prefill_kernel():
+class _TorchRecordingTopk:
+    """Stands in for the ``torch`` module inside the extracted functions: everything is torch's own,
+    except that the inputs of ``topk`` are kept."""
+
+    def __init__(self, sink: dict):
+        self._sink = sink
+
+    def __getattr__(self, name):
+        return getattr(torch, name)
+
+    def topk(self, x, *a, **kw):
+        self._sink.setdefault("topk_inputs", []).append(x.detach().clone())
+        return torch.topk(x, *a, **kw)
+
+
+def load_reference_prefill_kernel(record_scores: bool = False):
     """exec the reference's estimator functions on CPU with the attention call recorded."""
     path = os.path.join(REFERENCE, "minference", "modules", "minference_forward.py")
     tree = ast.parse(open(path).read())
@@ -114,7 +136,7 @@ def load_reference_prefill_kernel():
 
     ar = torch.arange(64)
     ns = {
-        "torch": torch, "math": math,
+        "torch": _TorchRecordingTopk(captured) if record_scores else torch, "math": math,
         "LAST_Q_MASK": ar[None, None, :, None] >= ar[None, None, None, :],
         "vertical_slash_sparse_attention": record,
         "streaming_forward": None, "block_sparse_attention": None,
@@ -145,6 +167,31 @@ def make_estimator_fixtures():
                             v_idx=captured["v_idx"].numpy(), s_idx=captured["s_idx"].numpy())
 
 
+ESTIMATOR_BF16_CASES = [  # (seed, n, vertical_size, slash_size)
+    (40, 600, 100, 200),
+    (41, 2048, 300, 700),
+    (42, 4096, 1000, 3000),
+    (43, 8192, 1000, 6096),
+]
+
+
+def make_estimator_bf16_fixtures():
+    from minference_b200.synthetic import make_qkv
+
+    kernel, captured = load_reference_prefill_kernel(record_scores=True)
+    for (seed, n, vs, ss) in ESTIMATOR_BF16_CASES:
+        q, k, v = make_qkv(n, 1, 1, seed=seed, dtype=torch.bfloat16)
+        cfg = {"best_pattern": [{"0": ["vertical_and_slash", vs, ss, 1.0]}]}
+        captured.pop("topk_inputs", None)
+        kernel(q, k, v, 0, 0, cfg)
+        vertical, slash = captured["topk_inputs"]           # [1,1,1,n] with the first 30 forced, [1,1,n] with the last 100 forced
+        np.savez_compressed(os.path.join(HERE, f"estimator_bf16_{seed}.npz"), n=n, vertical_size=vs, slash_size=ss,
+                            q_last_bits=q[0, 0, -64:].view(torch.int16).numpy(), k_bits=k[0, 0].view(torch.int16).numpy(),
+                            v_idx=captured["v_idx"].numpy(), s_idx=captured["s_idx"].numpy(),
+                            vertical_scores=vertical.float().reshape(-1).numpy(),
+                            slash_scores_by_offset=slash.float().reshape(-1).flip(0).numpy())
+
+
 BLOCK_CASES = [  # (seed, n, heads, top_k)
     (30, 512, 1, 3),
     (31, 1000, 1, 5),
@@ -171,10 +218,11 @@ def make_block_fixtures():
 
 def main():
     if not os.path.isdir(REFERENCE):
-        sys.exit(f"reference tree {REFERENCE} not found")
+        sys.exit("no reference tree: set MINFERENCE_REFERENCE to the checked-out tree")
     digests = {}
     make_index_fixtures(digests)
     make_estimator_fixtures()
+    make_estimator_bf16_fixtures()
     make_block_fixtures()
     with open(os.path.join(HERE, "digests.json"), "w") as f:
         json.dump(digests, f, indent=1, sort_keys=True)

@@ -24,19 +24,26 @@ def main():
     n, hq, hkv = 256 * 2 * world * 8, 8, 2
     q, k, v = make_qkv(n, hq, hkv, seed=3, dtype=torch.bfloat16)          # same tensors on every rank (CPU generator)
     q_loc, k_loc, v_loc = (ring.zigzag_split(t, rank, world).to(dev) for t in (q, k, v))
-    out_loc = ring.ring_vertical_slash_attention(q_loc, k_loc, v_loc, n, 200, 600)
+    stats = {}
+    out_loc = ring.ring_vertical_slash_attention(q_loc, k_loc, v_loc, n, 200, 600, stats=stats)
     gathered = [torch.empty_like(out_loc) for _ in range(world)]
     dist.all_gather(gathered, out_loc)
     ok = True
     if rank == 0:
+        from tests.test_gpu_ring import _one_rounding_apart
+
         merged = ring.zigzag_merge(gathered, world).float()
         dq, dk, dv = q.to(dev), k.to(dev), v.to(dev)
         v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(dq, dk, 200, 600)
+        # chunks are multiples of the 2048-key statistics block: the distributed estimator returns the very lists
+        # of the whole-sequence one, whatever the number of ranks
+        same_lists = torch.equal(stats["indices"][0], v_idx) and torch.equal(stats["indices"][1], s_idx)
         full = sparse_attention_forward(dq, dk, dv, build_vertical_slash_plan(v_idx, s_idx, n, nnz_v, nnz_s)).float()
         d = (merged - full).abs()
-        # the index sets may differ in a few near-ties (different summation order of the statistics)
-        print(f"ring vs whole-sequence: max {d.max().item():.3e} mean {d.mean().item():.3e}")
-        ok = d.mean().item() < 2e-3 and torch.isfinite(merged).all().item()
+        close = _one_rounding_apart(merged, full)       # merged in fp32 inside the kernel and rounded once
+        print(f"ring vs whole-sequence on {world} ranks, {n} tokens: index lists identical {same_lists}; "
+              f"max {d.max().item():.3e} mean {d.mean().item():.3e}; at most one bf16 step apart {close}")
+        ok = same_lists and close and d.max().item() < 1.5e-2 and torch.isfinite(merged).all().item()
     # per-head pattern table (vertical-slash and A-shape heads) through the ring against the single-GPU operator
     from minference_b200.modules.minference_forward import LayerPattern, minference_prefill_forward
 

@@ -10,7 +10,7 @@ from oracle import reference_math as R
 
 
 def test_estimator_matches_reference_fixtures(golden_dir):
-    paths = sorted(glob.glob(os.path.join(golden_dir, "estimator_*.npz")))
+    paths = sorted(glob.glob(os.path.join(golden_dir, "estimator_[0-9]*.npz")))
     assert len(paths) >= 4
     for path in paths:
         z = np.load(path)
@@ -28,6 +28,26 @@ def test_estimator_matches_reference_fixtures(golden_dir):
             assert set(range(min(30, n))) <= set(v_idx.flatten().tolist())
         if s_idx.numel() >= 100:
             assert set(range(100)) <= set(s_idx.flatten().tolist())
+
+
+def test_estimator_matches_reference_run_in_bf16(golden_dir):
+    """The reference's functions executed on bf16 tensors (the dtype of its GPU path): the restatement on the same
+    tensors returns the same lists and the same score vectors."""
+    paths = sorted(glob.glob(os.path.join(golden_dir, "estimator_bf16_*.npz")))
+    assert len(paths) >= 4
+    for path in paths:
+        z = np.load(path)
+        n = int(z["n"])
+        k = torch.from_numpy(z["k_bits"]).view(torch.bfloat16)[None, None]
+        q = torch.zeros(1, 1, n, 128, dtype=torch.bfloat16)
+        q[0, 0, -64:] = torch.from_numpy(z["q_last_bits"]).view(torch.bfloat16)
+        v_idx, s_idx, vsc, ssc = R.vertical_slash_estimate(q, k, int(z["vertical_size"]), int(z["slash_size"]), return_scores=True)
+        assert set(v_idx.flatten().tolist()) == set(z["v_idx"].flatten().tolist()), path
+        assert set(s_idx.flatten().tolist()) == set(z["s_idx"].flatten().tolist()), path
+        assert np.array_equal(vsc.float().numpy(), z["vertical_scores"])
+        got, want = ssc.float().flip(0).numpy(), z["slash_scores_by_offset"]       # the diagonal sums add in another order
+        fin = np.isfinite(want)
+        assert np.array_equal(np.isfinite(got), fin) and np.allclose(got[fin], want[fin], rtol=2e-6, atol=1e-9)
 
 
 def test_diagonal_sum_definition():
