@@ -189,12 +189,19 @@ int minf_vs_scores_pass(
     float* vertical_scores, float* slash_scores,
     int32_t* status, void* stream);
 int minf_vs_scores_combine(const void* stats, int batch, int hq, int blocks_total, void* row_stats, void* stream);
-/* `scratch` holds minf_vs_select_scratch_bytes() bytes (histograms and per-segment counts). */
+/*
+ * Per-head top-k over the score arrays.  The first `force_columns` keys and the `force_diagonals` nearest
+ * diagonals are always taken and budgets are raised to `min_vertical` / `min_slash`: 30, 100, 30, 50 for the
+ * online path (minference_forward.py:600, :608, :612), 30, 30, 30, 50 for its static variant (:421, :433) and
+ * 30, 30, 0, 0 for the offline search (:140-146).  `scratch` holds minf_vs_select_scratch_bytes() bytes
+ * (histograms and per-segment counts).
+ */
 size_t minf_vs_select_scratch_bytes(int batch, int hq, int context_size);
 int minf_vs_select(
     const float* vertical_scores, const float* slash_scores, int batch, int hq, int context_size,
     const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
-    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* scratch, void* stream);
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
+    int force_columns, int force_diagonals, int min_vertical, int min_slash, void* scratch, void* stream);
 
 /*
  * minf_vs_estimate for callers that cannot provide scratch memory and must not trigger an

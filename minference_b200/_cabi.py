@@ -19,6 +19,8 @@ LIB_PATH = os.path.join(_HERE, "libminfer_b200.so")
 STATUS_WORDS = 4
 ST_ERROR, ST_NO_SLASH = 0, 1
 MODE_PLAN, MODE_ASHAPE = 0, 1
+# (force_columns, force_diagonals, min_vertical, min_slash) of minf_vs_select
+SELECT_RULES = {"online": (30, 100, 30, 50), "static": (30, 30, 30, 50), "search": (30, 30, 0, 0)}
 
 _lib = None
 
@@ -47,7 +49,7 @@ SIGNATURES = {
     "minf_vs_scores_combine": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "minf_vs_select_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_select": (c_int, [c_void_p, c_void_p] + [c_int] * 3 + [c_void_p, c_void_p, c_int, c_int] +
-                       [c_void_p] * 4 + [c_void_p, c_void_p]),
+                       [c_void_p] * 4 + [c_int] * 4 + [c_void_p, c_void_p]),
     "minf_vs_estimate_static_scratch_limit": (c_size_t, []),
     "minf_vs_estimate_static": (c_int, [c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 5 + [c_void_p] * 2 +
                                 [c_int, c_int] + [c_void_p] * 4 + [c_void_p, c_void_p]),

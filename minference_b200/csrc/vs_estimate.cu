@@ -400,6 +400,8 @@ struct SelectArgs {
     const int32_t* vertical_size;   // per head budgets before clamping
     const int32_t* slash_size;
     int cap_v, cap_s;
+    int force_columns, force_diagonals;   // the first columns / nearest diagonals that are always taken
+    int min_vertical, min_slash;          // budgets are raised to these
     int32_t* v_idx;
     int32_t* s_idx;
     int32_t* nnz_v;
@@ -411,13 +413,14 @@ struct SelectArgs {
 
 // value of element `pos` in iteration order, with the forced +inf entries applied
 //   vertical: pos = key index, first 30 forced          (minference_forward.py:608)
-//   slash:    pos = N-1-offset (the reference's order), offsets < 100 forced (:612)
-__device__ __forceinline__ uint32_t sel_key(const float* src, int pos, int n, bool is_slash) {
+//   slash:    pos = N-1-offset (the reference's order), offsets < 100 forced (:612; 30 in the static
+//             variant :433 and in the offline search :145)
+__device__ __forceinline__ uint32_t sel_key(const SelectArgs& a, const float* src, int pos, int n, bool is_slash) {
     if (is_slash) {
         const int off = n - 1 - pos;
-        return off < 100 ? 0x7f800000u : __float_as_uint(src[off]);
+        return off < a.force_diagonals ? 0x7f800000u : __float_as_uint(src[off]);
     }
-    return pos < 30 ? 0x7f800000u : __float_as_uint(src[pos]);
+    return pos < a.force_columns ? 0x7f800000u : __float_as_uint(src[pos]);
 }
 
 // list = 2 * (batch*heads index) + (0 vertical | 1 slash); returns k (or -1 when the head is skipped)
@@ -426,7 +429,7 @@ __device__ __forceinline__ int sel_list_k(const SelectArgs& a, int list) {
     const bool is_slash = list & 1;
     const int budget = is_slash ? a.slash_size[bh] : a.vertical_size[bh];
     if (budget < 0) return -1;
-    const int k = min(a.n_ctx, max(budget, is_slash ? 50 : 30));    // minference_forward.py:600
+    const int k = min(a.n_ctx, max(budget, is_slash ? a.min_slash : a.min_vertical));    // minference_forward.py:600
     return min(k, is_slash ? a.cap_s : a.cap_v);
 }
 
@@ -456,7 +459,7 @@ __global__ void __launch_bounds__(kSelThreads) vs_select_hist_kernel(const Selec
     for (int j = 0; j < kSelItems; ++j) {
         const int pos = p0 + j * kSelThreads + threadIdx.x;
         if (pos < n) {
-            const uint32_t key = sel_key(src, pos, n, is_slash);
+            const uint32_t key = sel_key(a, src, pos, n, is_slash);
             if ((key & kPrefixMask) == prefix) atomicAdd(&hist[(key >> kShift) & (kBins - 1)], 1u);
         }
     }
@@ -527,7 +530,7 @@ __global__ void __launch_bounds__(kSelThreads) vs_select_count_kernel(const Sele
     for (int j = 0; j < kSelItems; ++j) {
         const int pos = p0 + j * kSelThreads + threadIdx.x;
         if (pos < n) {
-            const uint32_t key = sel_key(src, pos, n, is_slash);
+            const uint32_t key = sel_key(a, src, pos, n, is_slash);
             gt += key > thr;
             eq += key == thr;
         }
@@ -579,7 +582,7 @@ __global__ void __launch_bounds__(kSelThreads) vs_select_write_kernel(const Sele
     const int p0 = seg * kSelSegment + threadIdx.x * kSelItems;
 #pragma unroll
     for (int j = 0; j < kSelItems; ++j) {
-        key[j] = p0 + j < n ? sel_key(src, p0 + j, n, is_slash) : 0u;
+        key[j] = p0 + j < n ? sel_key(a, src, p0 + j, n, is_slash) : 0u;
         gt += p0 + j < n && key[j] > thr;
         eq += p0 + j < n && key[j] == thr;
     }
@@ -697,12 +700,16 @@ extern "C" size_t minf_vs_select_scratch_bytes(int batch, int hq, int context_si
 extern "C" int minf_vs_select(
     const float* vertical_scores, const float* slash_scores, int batch, int hq, int context_size,
     const int32_t* vertical_size, const int32_t* slash_size, int cap_v, int cap_s,
-    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out, void* scratch, void* stream) {
+    int32_t* v_idx_out, int32_t* s_idx_out, int32_t* nnz_v_out, int32_t* nnz_s_out,
+    int force_columns, int force_diagonals, int min_vertical, int min_slash, void* scratch, void* stream) {
     if (!vertical_scores || !slash_scores || !vertical_size || !slash_size || !v_idx_out || !s_idx_out || !nnz_v_out ||
         !nnz_s_out || !scratch)
         return fail(MINF_E_ARG, "null pointer argument");
     if (batch < 1 || hq < 1 || context_size < 1 || cap_v < 1 || cap_s < 1) return fail(MINF_E_ARG, "bad sizes");
+    if (force_columns < 0 || force_diagonals < 0 || min_vertical < 0 || min_slash < 0) return fail(MINF_E_ARG, "bad selection rules");
     SelectArgs s{};
+    s.force_columns = force_columns; s.force_diagonals = force_diagonals;
+    s.min_vertical = min_vertical; s.min_slash = min_slash;
     s.lists = 2 * batch * hq; s.n_ctx = context_size;
     s.segments = (context_size + kSelSegment - 1) / kSelSegment;
     if (s.lists > 65535) return fail(MINF_E_UNSUPPORTED, "too many heads");
@@ -773,7 +780,7 @@ extern "C" int minf_vs_estimate(
                                   nullptr, 0, blocks, row_stats, vertical, slash, status, stream)))
         return rc;
     return minf_vs_select(vertical, slash, batch, hq, context_size, vertical_size, slash_size, cap_v, cap_s,
-                          v_idx_out, s_idx_out, nnz_v_out, nnz_s_out, sel_scratch, stream);
+                          v_idx_out, s_idx_out, nnz_v_out, nnz_s_out, 30, 100, 30, 50, sel_scratch, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -228,7 +228,7 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_
     with torch.cuda.device(dev):
         _cabi.check(L.minf_vs_select(_cabi.ptr(scores[0]), _cabi.ptr(scores[1]), B, H, n_ctx, _cabi.ptr(vs), _cabi.ptr(ss),
                                      cap_v, cap_s, _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
-                                     _cabi.ptr(scratch), _cabi.stream_ptr(dev)))
+                                     *_cabi.SELECT_RULES["online"], _cabi.ptr(scratch), _cabi.stream_ptr(dev)))
     _cabi.raise_on_status(status, "ring_vertical_slash_estimate")
     return v_idx, s_idx, nnz_v, nnz_s
 
@@ -254,6 +254,14 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None,
     c = chunk_size(n_ctx, world)
     B, H, _, D = q_loc.shape
     dev = q_loc.device
+    # every rank can check its own shard against the layout all ranks derive from (n_ctx, world): a rank with a
+    # wrong shard stops here, before it sends anything, and its neighbours' receives end in the group's timeout
+    for name, t in (("q_loc", q_loc), ("k_loc", k_loc), ("v_loc", v_loc)):
+        if t.shape[2] != 2 * c or t.shape[0] != B or t.shape[3] != D:
+            raise ValueError(f"{name} has shape {tuple(t.shape)}; rank {rank} of {world} owns two chunks of {c} tokens "
+                             f"of a {n_ctx}-token sequence")
+    if k_loc.shape != v_loc.shape:
+        raise ValueError(f"k_loc {tuple(k_loc.shape)} and v_loc {tuple(v_loc.shape)} differ")
     q_chunks = owned_chunks(rank, world)
     q_parts = [q_loc[:, :, :c], q_loc[:, :, c:]]
     acc_o = torch.empty((2, B, H, c, D), dtype=torch.float32, device=dev)

@@ -1,10 +1,11 @@
 """Configuration object of the patch API (mirrors minference/minference_configuration.py:7-111).
 
 Only the attention types that run on this library's kernels are accepted: the dynamic sparse
-prefill ("minference", also with ``is_search=True`` for the offline pattern search), the fixed A-shape
-pattern ("a_shape"), A-shape with dense last rows ("tri_shape") and dense causal ("dense").  The
-KV-cache methods of the reference (kv_type other than "dense") are decode-side features outside
-this library.
+prefill ("minference", also with ``is_search=True`` for the offline pattern search; "vllm_minference"
+for the vLLM hook), its static variant ("static"), the fixed index sets "dilated1" / "dilated2", the
+fixed A-shape pattern ("a_shape"), A-shape with dense last rows ("tri_shape"), the TriangleMix layer
+policies ("tri_mix", "tri_mix_minference") and dense causal ("dense").  The KV-cache methods of the
+reference (kv_type other than "dense") are decode-side features outside this library.
 """
 from __future__ import annotations
 
@@ -12,8 +13,8 @@ from .configs.model2path import MODEL2PATH
 
 
 class MInferenceConfig:
-    MINFERENCE_ATTENTION_TYPES = ["minference"]
-    OTHER_ATTENTION_TYPES = ["dense", "a_shape", "tri_shape"]
+    MINFERENCE_ATTENTION_TYPES = ["minference", "vllm_minference", "tri_mix_minference"]      # need a pattern table
+    OTHER_ATTENTION_TYPES = ["dense", "static", "dilated1", "dilated2", "a_shape", "tri_shape", "tri_mix"]
     KV_TYPES = ["dense"]
 
     def __init__(
@@ -46,6 +47,7 @@ class MInferenceConfig:
         self.kv_cache_cpu = kv_cache_cpu
         self.kv_cache_cpu_device = kv_cache_cpu_device
         self.kv_type = kv_type
+        print(f"<---- MInference Config Detail ----> attn_type {self.attn_type}, kv_type {self.kv_type}")   # as the reference (:64-66)
         self.attn_kwargs = {
             "is_search": is_search,
             "starting_layer": starting_layer,
@@ -54,10 +56,10 @@ class MInferenceConfig:
         }
 
     def update_config_path(self, config_path: str = None, model_name: str = None):
-        if self.attn_type in self.OTHER_ATTENTION_TYPES:
-            return ""
         if config_path is not None:
             return config_path
+        if self.attn_type in self.OTHER_ATTENTION_TYPES:
+            return MODEL2PATH.get(model_name, "")     # "static" reads head 0's budgets from a table when one is known
         if model_name not in MODEL2PATH:
             raise ValueError(
                 f"No pattern table is registered for {model_name}: pass config_path=... (the JSON schema is "

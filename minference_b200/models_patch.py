@@ -30,19 +30,40 @@ class MInference:
     def patch_model(self, model):
         model.config.starting_layer = self.config.starting_layer
         model.config.config_path = self.config.config_path
-        if self.config.attn_type == "minference":
-            # the pattern table is loaded once here (models_patch.py:98-102 of the reference)
+        kw = self.config.attn_kwargs
+        ty = self.config.attn_type
+
+        def load_table():       # the pattern table is loaded once here (models_patch.py:98-102 of the reference)
+            if "best_pattern" not in kw:
+                with open(self.config.config_path, "r") as f:
+                    kw["best_pattern"] = json.load(f)
+
+        if ty in ("minference", "vllm_minference"):
             if self.config.is_search:
                 # every prefill call searches its layer and appends to config_path; layers run dense meanwhile
-                self.config.attn_kwargs["config_path"] = self.config.config_path
-            elif "best_pattern" not in self.config.attn_kwargs:
-                with open(self.config.config_path, "r") as f:
-                    self.config.attn_kwargs["best_pattern"] = json.load(f)
-            if self.config.attn_kwargs.get("starting_layer", -1) < 0:
-                self.config.attn_kwargs["starting_layer"] = 0
-        elif self.config.attn_type in ("a_shape", "tri_shape"):
-            self.config.attn_kwargs.setdefault("n_local", 3968)
-            self.config.attn_kwargs.setdefault("n_init", 128)
-            if self.config.attn_type == "tri_shape":
-                self.config.attn_kwargs.setdefault("n_last", 100)
+                kw["config_path"] = self.config.config_path
+            else:
+                load_table()
+            if kw.get("starting_layer", -1) < 0:
+                kw["starting_layer"] = 0
+        elif ty in ("tri_mix", "tri_mix_minference"):       # defaults of the reference (:103-128)
+            if ty == "tri_mix_minference":
+                load_table()
+            kw.setdefault("n_local", 512)
+            kw.setdefault("n_init", 8)
+            kw.setdefault("n_last", 128)
+            if kw.get("starting_layer", -1) < 0:
+                kw["starting_layer"] = 16
+        elif ty in ("a_shape", "tri_shape"):
+            kw.setdefault("n_local", 3968)
+            kw.setdefault("n_init", 128)
+            if ty == "tri_shape":
+                kw.setdefault("n_last", 100)
+        elif ty == "static":
+            if self.config.config_path:       # budgets of head 0 come from the table; without one the default (1000, 6096)
+                load_table()
+        if ty == "vllm_minference":
+            from .vllm_hook import patch_vllm
+
+            return patch_vllm(model, self.config)
         return new_patch(model, self.config)

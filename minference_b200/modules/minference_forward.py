@@ -68,16 +68,40 @@ def vertical_slash_estimate(query, key, vertical_size, slash_size, cap_v=None, c
     return v_idx, s_idx, nnz_v, nnz_s
 
 
+def vertical_slash_select(vertical_scores, slash_scores, vertical_size, slash_size, cap_v: int, cap_s: int,
+                          rules: str = "online"):
+    """Per-head top-k over score arrays ``[B,H,N]`` (as ``vertical_slash_estimate(return_scores=True)`` returns
+    them) under one of the reference's rule sets: ``online`` (first 30 columns and the 100 nearest diagonals
+    forced, budgets raised to 30 / 50), ``static`` (30 diagonals forced) or ``search`` (30 diagonals forced,
+    budgets taken as they are).  Budgets: int32 tensors ``[B*H]``."""
+    B, H, N = vertical_scores.shape
+    dev = vertical_scores.device
+    L = _cabi.lib()
+    v_idx = torch.empty((B, H, cap_v), dtype=torch.int32, device=dev)
+    s_idx = torch.empty((B, H, cap_s), dtype=torch.int32, device=dev)
+    nnz_v = torch.empty((B * H,), dtype=torch.int32, device=dev)
+    nnz_s = torch.empty((B * H,), dtype=torch.int32, device=dev)
+    scratch = torch.empty(L.minf_vs_select_scratch_bytes(B, H, N), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(L.minf_vs_select(
+            _cabi.ptr(vertical_scores), _cabi.ptr(slash_scores), B, H, N, _cabi.ptr(vertical_size), _cabi.ptr(slash_size),
+            cap_v, cap_s, _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s),
+            *_cabi.SELECT_RULES[rules], _cabi.ptr(scratch), _cabi.stream_ptr(dev)))
+    return v_idx, s_idx, nnz_v, nnz_s
+
+
 class LayerPattern:
     """Per-head pattern of one layer, parsed once from the JSON table entry
     ``{str(head): [type, vertical, slash, score]}`` (configs/*.json of the reference)."""
 
-    def __init__(self, layer_cfg: dict, num_heads: int, n_ctx: int, ratio: float | None, device):
+    def __init__(self, layer_cfg: dict, num_heads: int, n_ctx: int, ratio: float | None, device, head_offset: int = 0):
+        """``head_offset``: index of this process's first head in the table -- under tensor parallelism a rank
+        holds ``num_heads`` consecutive heads starting at ``rank * num_heads`` (minference_forward.py:902)."""
         modes, params, vsz, ssz, bsel = [], [], [], [], []
         self.cap_v, self.cap_s = 1, 1
         self.any_vs = self.any_bs = False
         for h in range(num_heads):
-            ty, v, s, _ = layer_cfg.get(str(h), DEFAULT_PATTERN)
+            ty, v, s, _ = layer_cfg.get(str(head_offset + h), DEFAULT_PATTERN)
             if ratio is not None:
                 v, s = int(v * ratio), int(s * ratio)
             if ty == "stream_llm":          # streaming_forward(q, k, v, n_init=v, n_local=s) (:626-631)
@@ -99,16 +123,22 @@ class LayerPattern:
         self.any_plan = self.any_vs or self.any_bs
 
 
-_PATTERN_CACHE: dict = {}
+_PATTERN_CACHE_ENTRIES = 256
 
 
-def _layer_pattern(cfg: dict, layer_idx: int, num_heads: int, n_ctx: int, device) -> LayerPattern:
+def _layer_pattern(cfg: dict, layer_idx: int, num_heads: int, n_ctx: int, device, head_offset: int = 0) -> LayerPattern:
+    """Device tables of one layer's pattern, parsed once per (layer, heads, length).  The cache lives inside the
+    attention config it was built from (so it dies with it and never serves another model's table) and keeps the
+    most recently used entries only."""
     ratio = cfg.get("minference_ratio") if "minference_ratio" in cfg else None
-    key = (id(cfg["best_pattern"]), layer_idx, num_heads, n_ctx, ratio, str(device))
-    pat = _PATTERN_CACHE.get(key)
+    cache = cfg.setdefault("_layer_patterns", {})
+    key = (layer_idx, num_heads, n_ctx, ratio, str(device), head_offset)
+    pat = cache.pop(key, None)
     if pat is None:
-        pat = LayerPattern(cfg["best_pattern"][layer_idx], num_heads, n_ctx, ratio, device)
-        _PATTERN_CACHE[key] = pat
+        pat = LayerPattern(cfg["best_pattern"][layer_idx], num_heads, n_ctx, ratio, device, head_offset)
+        while len(cache) >= _PATTERN_CACHE_ENTRIES:
+            cache.pop(next(iter(cache)))
+    cache[key] = pat          # most recently used last
     return pat
 
 
@@ -116,6 +146,8 @@ def minference_prefill_forward(query_states, key_states, value_states, prefill_k
     """Same call as the reference (minference_forward.py:633-674): ``[B,H,N,D]`` in,
     ``[B,H,N,D]`` out.  ``key_states`` / ``value_states`` may carry either the query head
     count (already repeated, as the reference's caller passes them) or the KV head count.
+    ``prefill_kwargs["head_offset"]`` (optional) is the table index of the first local head when the
+    heads are sharded over tensor-parallel ranks.
     """
     cfg = prefill_kwargs["attn_forward_config"]
     starting_layer = cfg.get("starting_layer", 0)
@@ -132,11 +164,9 @@ def minference_prefill_forward(query_states, key_states, value_states, prefill_k
                           prefill_kwargs.get("num_hidden_layers", 0), cfg.get("config_path"))
 
     if is_search or layer_idx < starting_layer:          # dense causal layers (:665-666)
-        mode = torch.full((H,), _cabi.MODE_ASHAPE, dtype=torch.int32, device=dev)
-        param = torch.tensor([[0, N]] * H, dtype=torch.int32, device=dev)
-        return sparse_attention_forward(query_states, key_states, value_states, None, head_mode=mode, head_param=param)
+        return dense_prefill_forward(query_states, key_states, value_states)
 
-    pat = _layer_pattern(cfg, layer_idx, H, N, dev)
+    pat = _layer_pattern(cfg, layer_idx, H, N, dev, int(prefill_kwargs.get("head_offset", 0)))
     plan = None
     if pat.any_plan:
         L = _cabi.lib()
@@ -170,3 +200,47 @@ def build_vertical_slash_plan_into(plan: SparsePlan, v_idx, s_idx, nnz_v, nnz_s)
             plan.batch, plan.heads, plan.context_size, plan.cap_v, plan.cap_s,
             _cabi.ptr(plan.plan), _cabi.ptr(plan.status), _cabi.stream_ptr(dev)))
     return v_idx
+
+
+def static_prefill_forward(query_states, key_states, value_states, prefill_kwargs):
+    """The reference's static variant (``vertical_and_slash_kernel_static``, minference_forward.py:418-437):
+    the index lists are estimated once per layer -- by the first head that runs, with that head's budgets, the
+    first 30 columns and only the 30 nearest diagonals forced -- and kept: every head of the layer, and every
+    later prompt, attends through the same vertical columns and diagonals.  The lists live in the attention
+    config (the reference keeps them on the attention module); a prompt of another length estimates again,
+    since indices beyond the new length would point outside it.
+    """
+    cfg = prefill_kwargs["attn_forward_config"]
+    layer_idx = prefill_kwargs["layer_idx"]
+    _cabi.require_cuda(query_states, key_states, value_states)
+    B, H, N, D = query_states.shape
+    assert B == 1, "the estimator of the reference is defined for batch 1"
+    dev = query_states.device
+    cache = cfg.setdefault("_static_vs", {})
+    entry = cache.get(layer_idx)
+    if entry is None or entry[0] != N:
+        table = cfg.get("best_pattern") or []
+        layer_cfg = table[layer_idx] if layer_idx < len(table) else {}
+        _, vs, ss, _ = layer_cfg.get("0", DEFAULT_PATTERN)
+        q0, k0 = query_states[:, :1], key_states[:, :1]        # query head 0 reads KV head 0, repeated or not
+        cap_v, cap_s = clamp_budgets(N, vs, ss)
+        *_, vsc, ssc = vertical_slash_estimate(q0, k0, vs, ss, return_scores=True)
+        budget = lambda x: torch.full((1,), x, dtype=torch.int32, device=dev)
+        v_idx, s_idx, _, _ = vertical_slash_select(vsc, ssc, budget(vs), budget(ss), cap_v, cap_s, rules="static")
+        entry = (N, v_idx.expand(B, H, -1).contiguous(), s_idx.expand(B, H, -1).contiguous())
+        cache[layer_idx] = entry
+    _, v_idx, s_idx = entry
+    plan = build_vertical_slash_plan(v_idx, s_idx, N)
+    out = sparse_attention_forward(query_states, key_states, value_states, plan)
+    if _status_checks_enabled():
+        _cabi.raise_on_status(plan.status, "static_prefill_forward")
+    return out
+
+
+def dense_prefill_forward(query_states, key_states, value_states):
+    """Plain causal attention through the same kernel (an A-shape window as long as the sequence)."""
+    H, N = query_states.shape[1], query_states.shape[2]
+    dev = query_states.device
+    mode = torch.full((H,), _cabi.MODE_ASHAPE, dtype=torch.int32, device=dev)
+    param = torch.tensor([[0, N]] * H, dtype=torch.int32, device=dev)
+    return sparse_attention_forward(query_states, key_states, value_states, None, head_mode=mode, head_param=param)

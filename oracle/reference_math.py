@@ -126,10 +126,11 @@ def sum_all_diagonal_matrix(mat: torch.Tensor) -> torch.Tensor:
 
 
 def vertical_slash_estimate(q: torch.Tensor, k: torch.Tensor, vertical_size: int, slash_size: int,
-                            return_scores: bool = False):
+                            return_scores: bool = False, forced_diagonals: int = 100):
     """Per-head index estimation, ``q,k`` of shape ``[1,1,N,D]`` (minference_forward.py:599-614).
 
     Returns ``(vertical_topk [1,1,1,v] int64, slash [1,1,s] int64 diagonal offsets)``.
+    ``forced_diagonals=30`` gives the static variant (``vertical_and_slash_kernel_static``, :418-437).
     """
     q_len = q.shape[2]
     head_dim = q.shape[-1]
@@ -145,7 +146,7 @@ def vertical_slash_estimate(q: torch.Tensor, k: torch.Tensor, vertical_size: int
     vertical[..., :30] = torch.inf
     vertical_topk = torch.topk(vertical, vertical_size, -1).indices
     slash = sum_all_diagonal_matrix(p)[..., : -last_q + 1]
-    slash[..., -100:] = torch.inf
+    slash[..., -forced_diagonals:] = torch.inf
     slash_idx = (q_len - 1) - torch.topk(slash, slash_size, -1).indices
     if return_scores:
         return vertical_topk, slash_idx, vertical[0, 0, 0], slash[0, 0]

@@ -123,8 +123,8 @@ def test_sharded_estimator_stages_match_whole_sequence(dev, n, world):
     nnz_s = torch.empty(hq, dtype=torch.int32, device=dev)
     scratch = torch.empty(L.minf_vs_select_scratch_bytes(1, hq, n), dtype=torch.uint8, device=dev)
     _cabi.check(L.minf_vs_select(_cabi.ptr(scores[0]), _cabi.ptr(scores[1]), 1, hq, n, _cabi.ptr(vsz), _cabi.ptr(ssz), 200, 600,
-                                 _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s), _cabi.ptr(scratch),
-                                 _cabi.stream_ptr(dev)))
+                                 _cabi.ptr(v_idx), _cabi.ptr(s_idx), _cabi.ptr(nnz_v), _cabi.ptr(nnz_s), *_cabi.SELECT_RULES["online"],
+                                 _cabi.ptr(scratch), _cabi.stream_ptr(dev)))
     if c % 2048 == 0:
         assert torch.equal(scores[0], vs_ref) and torch.equal(scores[1], ss_ref)
         assert torch.equal(v_idx, v_ref) and torch.equal(s_idx, s_ref)

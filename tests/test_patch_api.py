@@ -28,6 +28,115 @@ def test_config_mirrors_reference_fields(tmp_path):
         MInferenceConfig(attn_type="inf_llm")
     with pytest.raises(ValueError):
         MInferenceConfig(kv_type="snapkv", config_path=str(path))
+    for ty in ("static", "tri_mix", "dilated1", "dilated2", "a_shape", "tri_shape", "dense"):       # no table needed
+        assert MInferenceConfig(attn_type=ty).attn_type == ty
+    assert MInferenceConfig(attn_type="tri_mix_minference", config_path=str(path)).config_path == str(path)
+    with pytest.raises(ValueError):
+        MInferenceConfig(attn_type="tri_mix_minference", model_name="no/such-model")
+
+
+def test_register_config_dir_maps_the_reference_model_names(tmp_path):
+    """MInference("minference", model_name) needs the model-name -> table-file mapping of the reference."""
+    from minference_b200 import MInferenceConfig
+    from minference_b200.configs import model2path as P
+
+    assert len(P.TABLE_FILE_OF_MODEL) == 18
+    fname = P.TABLE_FILE_OF_MODEL["gradientai/Llama-3-8B-Instruct-Gradient-1048k"]
+    assert fname == P.TABLE_FILE_OF_MODEL["gradientai/Llama-3-8B-Instruct-262k"] and fname.endswith("best_pattern.json")
+    (tmp_path / fname).write_text(json.dumps([{"0": ["vertical_and_slash", 30, 800, 0.9]}]))
+    saved = dict(P.MODEL2PATH)
+    try:
+        names = P.register_config_dir(str(tmp_path))
+        assert sorted(names) == sorted(m for m, f in P.TABLE_FILE_OF_MODEL.items() if f == fname)
+        cfg = MInferenceConfig("minference", model_name="gradientai/Llama-3-8B-Instruct-Gradient-1048k")
+        assert cfg.config_path == str(tmp_path / fname)
+        with pytest.raises(ValueError):
+            MInferenceConfig("minference", model_name="Qwen/Qwen2.5-7B-Instruct")       # its file is not in the directory
+        assert len(P.register_config_dir(str(tmp_path), require_files=False)) == 18
+    finally:
+        P.MODEL2PATH.clear()
+        P.MODEL2PATH.update(saved)
+
+
+def test_patch_defaults_follow_the_reference(tmp_path, monkeypatch):
+    """Per-type defaults injected by MInference.patch_model (models_patch.py:98-128 of the reference)."""
+    import types
+
+    from minference_b200 import MInference, models_patch
+
+    monkeypatch.setattr(models_patch, "new_patch", lambda model, cfg: cfg)
+    model = types.SimpleNamespace(config=types.SimpleNamespace())
+    path = tmp_path / "t.json"
+    path.write_text(json.dumps([{"0": ["vertical_and_slash", 30, 800, 0.9]}]))
+    kw = MInference("tri_mix")(model).attn_kwargs
+    assert (kw["n_local"], kw["n_init"], kw["n_last"], kw["starting_layer"]) == (512, 8, 128, 16)
+    kw = MInference("tri_mix_minference", config_path=str(path), starting_layer=3)(model).attn_kwargs
+    assert kw["starting_layer"] == 3 and kw["best_pattern"][0]["0"][1] == 30
+    kw = MInference("tri_shape")(model).attn_kwargs
+    assert (kw["n_local"], kw["n_init"], kw["n_last"]) == (3968, 128, 100)
+    kw = MInference("static", config_path=str(path))(model).attn_kwargs
+    assert kw["best_pattern"][0]["0"][2] == 800
+    assert "best_pattern" not in MInference("static")(model).attn_kwargs
+
+
+def test_layer_pattern_cache_is_bounded_and_tied_to_its_config():
+    from minference_b200.modules import minference_forward as mf
+
+    table = [{"0": ["stream_llm", 64, 256, 1.0]}]
+    cfg_a = {"best_pattern": table}
+    pa = mf._layer_pattern(cfg_a, 0, 2, 1024, "cpu")
+    assert mf._layer_pattern(cfg_a, 0, 2, 1024, "cpu") is pa            # same config, same key: reused
+    cfg_b = {"best_pattern": [{"0": ["stream_llm", 8, 16, 1.0]}]}        # another model's table, same layer / heads / length
+    pb = mf._layer_pattern(cfg_b, 0, 2, 1024, "cpu")
+    assert pb is not pa and pb.head_param.tolist()[0] == [8, 16] and pa.head_param.tolist()[0] == [64, 256]
+    for n in range(mf._PATTERN_CACHE_ENTRIES + 40):                      # many prompt lengths: the cache stays bounded
+        mf._layer_pattern(cfg_a, 0, 2, 2048 + 64 * n, "cpu")
+    assert len(cfg_a["_layer_patterns"]) <= mf._PATTERN_CACHE_ENTRIES
+    off = mf.LayerPattern({"0": ["stream_llm", 1, 2, 1], "3": ["stream_llm", 5, 6, 1]}, 2, 1024, None, "cpu", head_offset=2)
+    assert off.head_param.tolist() == [[0, 0], [5, 6]] and off.vertical_size.tolist()[0] == 1000     # heads 2 and 3 of the table
+
+
+def test_stock_attention_is_used_when_the_sparse_kernels_do_not_apply():
+    """Another logit scale, sliding-window layers, batch above 1, another dtype: the registered attention function
+    must hand the call to the stock implementation instead of computing with 1/sqrt(d)."""
+    from minference_b200.patch import _sparse_path_refusal
+
+    q = torch.zeros(1, 4, 512, 128, dtype=torch.bfloat16, device="meta")
+    ok = lambda **kw: _sparse_path_refusal(kw.pop("q", q), kw.pop("k", q), kw.pop("scaling", None), kw)
+    cuda_like = type("T", (), {"shape": q.shape, "dtype": torch.bfloat16, "is_cuda": True, "device": torch.device("cuda")})()
+    assert _sparse_path_refusal(cuda_like, cuda_like, None, {}) is None
+    assert _sparse_path_refusal(cuda_like, cuda_like, 128 ** -0.5, {}) is None
+    assert "scales" in _sparse_path_refusal(cuda_like, cuda_like, 0.0078125, {})              # Granite-style multiplier
+    assert "sliding" in _sparse_path_refusal(cuda_like, cuda_like, None, {"sliding_window": 4096})
+    assert "soft" in _sparse_path_refusal(cuda_like, cuda_like, None, {"softcap": 50.0})
+    assert "bf16" in ok()                                                                      # not a CUDA tensor
+    one = type("T", (), {"shape": (1, 4, 1, 128), "dtype": torch.bfloat16, "is_cuda": True, "device": torch.device("cuda")})()
+    assert _sparse_path_refusal(one, cuda_like, None, {}) == "decode"
+    two = type("T", (), {"shape": (2, 4, 512, 128), "dtype": torch.bfloat16, "is_cuda": True, "device": torch.device("cuda")})()
+    assert "batch" in _sparse_path_refusal(two, two, None, {})
+
+
+def test_vllm_hook_recognises_a_single_sequence_prefill():
+    import types
+
+    from minference_b200 import vllm_hook as V
+
+    assert V.layer_index_of("model.layers.17.self_attn.attn") == 17 and V.layer_index_of("3.attn") == 3
+    md = lambda n, seqs, max_q, max_s, **kw: types.SimpleNamespace(
+        num_actual_tokens=n, query_start_loc=torch.zeros(seqs + 1, dtype=torch.int32), max_query_len=max_q, max_seq_len=max_s,
+        use_cascade=kw.get("cascade", False), causal=kw.get("causal", True))
+    assert V.is_single_sequence_prefill(md(4096, 1, 4096, 4096))
+    assert not V.is_single_sequence_prefill(md(4096, 2, 2048, 2048))        # two requests
+    assert not V.is_single_sequence_prefill(md(1024, 1, 1024, 5120))        # a later chunk: cached context
+    assert not V.is_single_sequence_prefill(md(1, 1, 1, 900))               # decode
+    assert not V.is_single_sequence_prefill(md(4096, 1, 4096, 4096, cascade=True))
+    assert not V.is_single_sequence_prefill(None)
+    impl = types.SimpleNamespace(head_size=128, scale=128 ** -0.5, alibi_slopes=None, sliding_window=(-1, -1),
+                                 logits_soft_cap=0, sinks=None)
+    q = types.SimpleNamespace(dtype=torch.bfloat16, is_cuda=True)
+    assert V.supports(impl, q)
+    impl.sliding_window = (4095, 0)
+    assert not V.supports(impl, q)
 
 
 def test_layer_pattern_parsing():

@@ -162,3 +162,51 @@ def test_sequence_sharded_whole_model_prefill_on_gloo_ranks():
         p.join(timeout=240)
         assert p.exitcode == 0
     assert result.get(timeout=10) < 1e-3
+
+
+# ------------------------------------------------------------------ failures among the ranks (host side only)
+
+def _failing_worker(rank, world, port, n, mode, result):
+    """One rank leaves before the exchange (an exception before its send) or brings a shard of another shape: the
+    others must come back with an error from their next collective instead of waiting for ever.  No GPU is
+    involved; the process group has a short timeout."""
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    outcome = "finished"
+    try:
+        q = torch.randn(1, 2, n, 16)
+        q_loc, k_loc, v_loc = (ring.zigzag_split(t, rank, world) for t in (q, q, q))
+        if mode == "raise" and rank == 1:
+            raise RuntimeError("rank 1 gives up before the ring")
+        if mode == "shape" and rank == 1:
+            k_loc, v_loc = k_loc[:, :, :-256].contiguous(), v_loc[:, :, :-256].contiguous()       # a shard that lost a block
+        out = ring.ring_attention(q_loc, k_loc, v_loc, n, _dense_window)
+        outcome = "finished" if torch.isfinite(out).all() else "non-finite"
+    except Exception as e:       # the point of the test: an exception on the host, not a hang
+        outcome = "error: " + type(e).__name__
+    finally:
+        result.put((rank, outcome))
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("mode", ["raise", "shape"])
+def test_a_rank_that_fails_before_its_send_ends_the_ring_with_an_error(mode):
+    world, n = 2, 256 * 4
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, n, mode, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode is not None, "a rank is still waiting: the failure was not detected"
+    outcomes = dict(result.get(timeout=10) for _ in range(world))
+    assert outcomes[1].startswith("error")
+    assert outcomes[0].startswith("error"), outcomes       # the healthy rank saw the failure as an exception
