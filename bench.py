@@ -50,7 +50,14 @@ WORKLOADS = {
 # vertical_slash_sparse_attention (no estimator in the step).  Seeded N(0,1) data has a nearly flat
 # slash score, so its estimated diagonals scatter over the whole context; heads of real models pick bands.
 LOCAL_WORKLOADS = {name + "_local": spec for name, spec in WORKLOADS.items()}
+# ... and with a prescribed scattered set: the 100 nearest diagonals + diagonals drawn uniformly from the whole
+# context (what the estimator returns on structureless data at a million tokens), at any length
+# (the number of drawn diagonals is scaled with the length so that their density is that of 6096 in a million)
+SCATTERED_WORKLOADS = {name + "_scattered": (n, hq, hkv, v, 100 + round((s - 100) * n / 1048576))
+                       for name, (n, hq, hkv, v, s) in WORKLOADS.items()}
 WORKLOADS.update(LOCAL_WORKLOADS)
+WORKLOADS.update(SCATTERED_WORKLOADS)
+LOCAL_WORKLOADS.update(SCATTERED_WORKLOADS)       # both are "prescribed index set" workloads
 # per-head mix of the three patterns (seeded): A-shape(128, 4096) / vertical-slash(1000, 6096) / block-sparse top-100
 MIXED_WORKLOADS = {
     "qwen25_7b_256k_mixed": (262144, 28, 4, 1000, 6096),
@@ -100,6 +107,7 @@ def workload_config(wl: str, world: int) -> dict:
     cfg = {"workload": wl, "tokens": n, "q_heads": hq, "kv_heads": hkv, "head_dim": 128, "vertical": vsize, "slash": ssize,
            "last_q": 64, "l2": "inputs_exceed_l2",
            "index_set": "band: slash offsets 0..s-1 + seeded vertical columns, given to the operator" if "_local" in wl
+           else "scattered: 100 nearest + uniformly drawn diagonals and columns, given to the operator" if "_scattered" in wl
            else "estimated online from the last 64 queries"}
     if ring:
         cfg["parallelism"] = f"one sequence, zigzag ring over {world} ranks, K/V shards by NCCL send/recv"
@@ -246,7 +254,7 @@ def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=No
     from minference_b200.ops.block_sparse_flash_attention import build_block_sparse_plan
     from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
     from minference_b200.ops.sparse_forward import SparsePlan, sparse_attention_forward
-    from minference_b200.synthetic import local_vs_indices, make_qkv
+    from minference_b200.synthetic import local_vs_indices, make_qkv, scattered_vs_indices
 
     if q is None:
         q, k, v = make_qkv(n, hq, hkv, seed=seed, dtype=torch.bfloat16, device=dev)
@@ -260,8 +268,9 @@ def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=No
         mixed_plan = SparsePlan(plan=torch.zeros(_cabi.lib().minf_plan_bytes(1, hq, n, pat.cap_v, pat.cap_s), dtype=torch.uint8, device=dev),
                                 v_idx=None, cap_v=pat.cap_v, cap_s=pat.cap_s, context_size=n, batch=1, heads=hq,
                                 status=_cabi.new_status(dev))
-    elif kind == "band":
-        bv, bs = local_vs_indices(n, hq, vsize, ssize, seed=seed, device=dev)
+    elif kind in ("band", "scattered"):
+        bv, bs = (scattered_vs_indices if kind == "scattered" else local_vs_indices)(n, hq, vsize, ssize, seed=seed, device=dev)
+        kind = "band"
         box["indices"] = (bv.contiguous(), bs.contiguous())
 
     def step(record: bool):
@@ -304,7 +313,7 @@ def issued_tiles_of(status) -> int:
 def side_measurement(name, dev, steps=2, warmup=1):
     """A short measurement of another single-GPU workload, reported inside ``detail`` of the headline line."""
     n, hq, hkv, vsize, ssize = WORKLOADS[name]
-    kind = "band" if name in LOCAL_WORKLOADS else "vs"
+    kind = "scattered" if name in SCATTERED_WORKLOADS else "band" if name in LOCAL_WORKLOADS else "vs"
     step, events, box, _ = layer_runner(n, hq, hkv, vsize, ssize, dev, 0, kind)
     for _ in range(warmup):
         step(False)
@@ -357,7 +366,8 @@ def run_gpu_arm(args, wl):
     mixed = wl in MIXED_WORKLOADS
     band = wl in LOCAL_WORKLOADS
     step_resident, events, box, (q, k, v) = layer_runner(n, hq, hkv, vsize, ssize, dev, rank,
-                                                         "mixed" if mixed else "band" if band else "vs")
+                                                         "mixed" if mixed else "scattered" if wl in SCATTERED_WORKLOADS
+                                                         else "band" if band else "vs")
     kinds = box["kinds"]
     table = box["table"] if mixed else {str(h): ["vertical_and_slash", vsize, ssize, 1.0] for h in range(hq)}
     cfg = {"attn_forward_config": {"best_pattern": [table]}, "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
@@ -765,7 +775,8 @@ def run_ttft_arm(args, wl):
     from minference_b200 import _cabi
     from minference_b200.cuda import set_status_checks
     from minference_b200.dist import ring
-    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables, zigzag_positions
+    from minference_b200.modules.minference_forward import LayerPattern
+    from minference_b200.prefill_runner import LlamaPrefill, LlamaShape, seeded_pattern_tables, split_times, zigzag_positions
 
     n, layers = TTFT_WORKLOADS[wl]
     rank = int(os.environ.get("RANK", "0"))
@@ -789,15 +800,13 @@ def run_ttft_arm(args, wl):
     logits_host = torch.empty(shape.vocab, dtype=torch.float32).pin_memory()
     attention = None
     if world > 1:       # with N > 1 ranks the prompt is sequence-sharded (zigzag chunks) and attention is the ring
-        from minference_b200.modules.minference_forward import LayerPattern
-
         patterns = [LayerPattern(t, shape.q_heads, n, None, dev) for t in tables]
         attention = lambda q, k, v, li: ring.ring_prefill_attention(q, k, v, n, patterns[li])
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def step():
+    def step(timing=None):
         ids = ids_host.to(dev, non_blocking=True)
-        logits = model.prefill(ids, cfg, positions=positions, attention=attention)
+        logits = model.prefill(ids, cfg, positions=positions, attention=attention, timing=timing)
         if rank == 0:       # the prompt's last token is rank 0's last token
             logits_host.copy_(logits, non_blocking=True)
 
@@ -807,18 +816,33 @@ def run_ttft_arm(args, wl):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
+    if args.short_warmup and args.warmup > 0:
+        # warm-up on a 32768-token prompt through the same code (kernels loaded, cuBLAS and NCCL initialised): a
+        # full-length warm-up step of a million-token prompt costs minutes of GPU time
+        n_short = 32768
+        ids_s = ids_all[:n_short]
+        pos_s = zigzag_positions(n_short, rank, world, dev) if world > 1 else None
+        att_s = None
+        if world > 1:
+            pats_s = [LayerPattern(t, shape.q_heads, n_short, None, dev) for t in tables[:2]]
+            att_s = lambda q, k, v, li: ring.ring_prefill_attention(q, k, v, n_short, pats_s[li % 2])
+        for _ in range(args.warmup):
+            model.prefill((ids_s[pos_s.cpu()] if world > 1 else ids_s).to(dev), cfg, positions=pos_s, attention=att_s)
+    else:
+        for _ in range(args.warmup):
+            step()
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
+    timing = {}
     t0, t1 = ev(), ev()
     t0.record()
     for _ in range(args.steps):
-        step()
+        step(timing)
     t1.record()
     barrier()
     clocks = sampler.stop() if sampler else None
-    t = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+    total_ms = t0.elapsed_time(t1)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ttft_s = t.item() / args.steps / 1e3
@@ -836,7 +860,9 @@ def run_ttft_arm(args, wl):
                        "head_patterns": {kd: kinds.count(kd) for kd in sorted(set(kinds))},
                        "parallelism": f"zigzag sequence split over {world} ranks, ring attention" if world > 1 else "one GPU",
                        "dense_gemm_pflop": dense_flop / 1e15, "dense_parts": "torch.matmul (cuBLAS), chunked over 16384 tokens",
-                       "tokens_per_s": n / ttft_s, "finite_logits": bool(torch.isfinite(logits_host).all())},
+                       "warmup_kind": "32768-token prompt" if args.short_warmup else "full prompt"},
+            "detail": {"tokens_per_s": n / ttft_s, "finite_logits": bool(torch.isfinite(logits_host).all()),
+                       "split_rank0": split_times(timing, total_ms / args.steps, layers)},
             "e2e": {"value": ttft_s, "unit": "s", "h2d_bytes_per_step": world * ids_host.numel() * ids_host.element_size(),
                     "d2h_bytes_per_step": logits_host.numel() * 4},
             "gpu_launches": None, "roofline": None, "cpu_baseline": None, "clocks": clocks,
@@ -853,6 +879,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(RING_WORKLOADS) + sorted(TTFT_WORKLOADS))
+    ap.add_argument("--short-warmup", action="store_true",
+                    help="whole-model workloads: warm up on a 32768-token prompt instead of the full one")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the side measurements reported beside the headline (band index set, the 1M-token layer on one GPU)")
     args = ap.parse_args()

@@ -34,7 +34,8 @@ extern "C" {
 #define MINF_ST_ERROR 0      /* bit 0: a device wait was abandoned; bit 1: misaligned smem; bit 2: bad plan (a head in
                                 plan mode without a plan, a range count beyond the slot's capacity, ranges that are
                                 not ascending and disjoint, or marked columns without a vertical list; the affected
-                                row blocks are computed from the part of the plan read before the fault) */
+                                row blocks are computed from the part of the plan read before the fault); bit 3: a
+                                range check of the debug build (-DMINF_BOUNDS) failed and the access was skipped */
 #define MINF_ST_NO_SLASH 1   /* number of row blocks whose slash list has no offset < end row */
 #define MINF_ST_AUX0 2        /* words 2-3, read as one uint64: 64x64 tile equivalents the attention kernel sent  */
 #define MINF_ST_AUX1 3        /* to the tensor pipe (its 128-row x 64/128-key steps), summed over launches         */

@@ -7,6 +7,7 @@ device pointers plus element strides; outputs and scratch are allocated here wit
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_ulonglong, c_void_p
@@ -14,7 +15,8 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libminfer_b200.so")
+# MINFER_B200_LIB selects another build of the same library (the range-checked debug variant of build.py --bounds)
+LIB_PATH = os.environ.get("MINFER_B200_LIB") or os.path.join(_HERE, "libminfer_b200.so")
 
 STATUS_WORDS = 4
 ST_ERROR, ST_NO_SLASH = 0, 1
@@ -64,6 +66,23 @@ SIGNATURES = {
 
 class MInferB200Error(RuntimeError):
     pass
+
+
+_NVTX = os.environ.get("MINFER_B200_NVTX", "0") == "1"
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """An NVTX range around a stage of the path (estimator, plan, attention, ring step) when MINFER_B200_NVTX=1,
+    so that a timeline profiler shows the stages by name; nothing otherwise."""
+    if not _NVTX:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 def lib():
@@ -118,7 +137,7 @@ def raise_on_status(status: torch.Tensor, what: str) -> None:
     st = status.tolist()
     if st[ST_ERROR]:
         raise MInferB200Error(f"{what}: device reported error bits {st[ST_ERROR]:#x} "
-                              "(1 = abandoned wait, 2 = misaligned shared memory, 4 = bad plan: a plan-mode head without a plan, "
+                              "(1 = abandoned wait, 2 = misaligned shared memory, 8 = a range check of the debug build failed, 4 = bad plan: a plan-mode head without a plan, "
                               "a range count beyond the slot's capacity, unordered ranges, or columns without a vertical list)")
     if st[ST_NO_SLASH]:
         raise MInferB200Error(f"{what}: {st[ST_NO_SLASH]} row blocks have no slash offset below their last row; "

@@ -34,16 +34,22 @@ def _newest_source_mtime() -> float:
     return t
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+LIB_BOUNDS = os.path.join(HERE, "libminfer_b200_bounds.so")
+
+
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> str:
+    """``bounds=True`` builds the range-checked debug variant (``-DMINF_BOUNDS``) as ``libminfer_b200_bounds.so``;
+    set ``MINFER_B200_LIB`` to its path to make the package load it."""
     srcs = [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source_mtime():
-        return LIB
+    lib = LIB_BOUNDS if bounds else LIB
+    if not force and os.path.exists(lib) and os.path.getmtime(lib) >= _newest_source_mtime():
+        return lib
     objs = []
     procs = []
     for s in srcs:
-        o = s[:-3] + ".o"
+        o = s[:-3] + (".bounds.o" if bounds else ".o")
         objs.append(o)
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", s, "-o", o]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DMINF_BOUNDS"] if bounds else []), "-c", s, "-o", o]
         procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for s, p in procs:
@@ -55,9 +61,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "static"])
-    return LIB
+    subprocess.check_call([_nvcc(), "-shared", "-o", lib, *objs, "-cudart", "static"])
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, bounds="--bounds" in sys.argv))

@@ -33,4 +33,13 @@ inline int fail(int code, const char* fmt, ...) {
             return ::minf::fail(MINF_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
     } while (0)
 
+// Range-checked debug build (-DMINF_BOUNDS, `python -m minference_b200.build --bounds`): every store of the index
+// kernels and every plan-derived coordinate of the attention kernel is checked against the capacity of its
+// destination; a violation sets bit 3 of status[MINF_ST_ERROR] and the access is skipped.  Nothing traps.
+#ifdef MINF_BOUNDS
+#define MINF_IN_BOUNDS(status, cond) ((cond) ? true : (atomicOr((status) + MINF_ST_ERROR, 8), false))
+#else
+#define MINF_IN_BOUNDS(status, cond) (true)
+#endif
+
 }  // namespace minf

@@ -337,6 +337,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         };
         auto load_tile = [&](int t, int width) -> bool {     // t: global position, inside the local key window
             const int lt = t - a.kv_pos0;
+            if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) return true;      // a tile that starts outside the local keys
             if (!wait_use(ctl->k_empty, kNK, step)) return false;
             if (lane == 0) {
                 const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
@@ -496,7 +497,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!publish(kGatherStep, 0, width, mk)) return;
                 int col[4];      // local key rows
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) col[q4] = val[q4] ? (e[q4] & 0x0fffffff) - a.kv_pos0 : 0;
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    col[q4] = val[q4] ? (e[q4] & 0x0fffffff) - a.kv_pos0 : 0;
+                    if (!MINF_IN_BOUNDS(a.status, col[q4] >= 0 && col[q4] < a.n_kv)) col[q4] = 0;
+                }
                 const int chunk = lane & 15, sub = lane >> 4;
                 const int iters = width / 2;
                 if (!wait_use(ctl->k_empty, kNK, step)) return;

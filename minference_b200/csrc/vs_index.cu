@@ -93,13 +93,14 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_convert_kernel(const Co
     if (i0 < nnz_s) {
         // close range [rs, re): emit its tiles, then advance through the verticals
         auto close_range = [&](int rs, int re) {
-            for (int t = rs + 64 * lane; t < re; t += 64 * 32) bo[nblk + ((t - rs) >> 6)] = t;
+            for (int t = rs + 64 * lane; t < re; t += 64 * 32)
+                if (MINF_IN_BOUNDS(a.status, nblk + ((t - rs) >> 6) < a.cap_s)) bo[nblk + ((t - rs) >> 6)] = t;
             nblk += (re - rs) >> 6;
             for (;;) {
                 const int i = vp + lane;
                 const int val = i < nnz_v ? v_list[i] : INT_MAX;
                 const int n_below = __popc(__ballot_sync(0xffffffffu, val < rs));
-                if (lane < n_below) ci[ncol + lane] = val;
+                if (lane < n_below && MINF_IN_BOUNDS(a.status, ncol + lane < a.cap_v)) ci[ncol + lane] = val;
                 ncol += n_below;
                 const int n_inside = __popc(__ballot_sync(0xffffffffu, val < re));
                 vp += n_inside;
@@ -204,7 +205,9 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
             // close range [rs, re): record it, then advance through the verticals; the columns below
             // rs that no earlier range covered are gathered: their bits span at most two words
             auto close_range = [&](int rs, int re) {
-                if (lane == 0) rng[nrng] = make_int2(rs, re);
+                // row block m of the sequence holds at most min(cap_s, m + 2) ranges (plan_layout.h)
+                if (lane == 0 && MINF_IN_BOUNDS(a.status, nrng < min(a.cap_s, a.rb_base + m + 2) && rs >= 0 && re > rs))
+                    rng[nrng] = make_int2(rs, re);
                 ++nrng;
                 for (;;) {
                     const int i = vp + lane;
@@ -214,6 +217,7 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
                         const int lo = vp, hi = vp + n_below;
                         const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
                         const int top = min(hi - 32 * w0, 32);
+                        if (!MINF_IN_BOUNDS(a.status, w1 < words_v)) break;
                         wb[w0] |= (top == 32 ? 0xffffffffu : ((1u << top) - 1u)) & ~((1u << (lo & 31)) - 1u);
                         if (w1 != w0) wb[w1] |= (hi - 32 * w1 == 32) ? 0xffffffffu : ((1u << (hi - 32 * w1)) - 1u);
                     }

@@ -283,6 +283,8 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None,
         src = (rank - step) % world
         reqs = []
         nxt = None
+        nvtx = _cabi.nvtx_range(f"ring:step{step}")
+        nvtx.__enter__()
         if step + 1 < world:       # pass the shard on while this step computes
             nxt = bufs[step % len(bufs)]
             ops = [dist.P2POp(dist.isend, kv[0], send_to, group), dist.P2POp(dist.isend, kv[1], send_to, group),
@@ -304,6 +306,7 @@ def ring_attention(q_loc, k_loc, v_loc, n_ctx: int, attn_fn: AttnFn, group=None,
                     merge_partial(acc_o[qi], acc_l[qi], o, lse)
         for r in reqs:
             r.wait()
+        nvtx.__exit__(None, None, None)
         if nxt is not None:
             kv = nxt               # the next receive into the other buffer set is ordered after this step's kernels
     if not fused_merge:

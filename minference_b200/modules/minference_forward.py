@@ -174,16 +174,19 @@ def minference_prefill_forward(query_states, key_states, value_states, prefill_k
         plan = SparsePlan(plan=torch.empty(nbytes, dtype=torch.uint8, device=dev), v_idx=None, cap_v=pat.cap_v,
                           cap_s=pat.cap_s, context_size=N, batch=B, heads=H, status=_cabi.new_status(dev))
         if pat.any_vs:
-            v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(
-                query_states, key_states, pat.vertical_size, pat.slash_size, cap_v=pat.cap_v, cap_s=pat.cap_s)
-            vs_plan = build_vertical_slash_plan_into(plan, v_idx, s_idx, nnz_v, nnz_s)
-            plan.v_idx = vs_plan
+            with _cabi.nvtx_range("minference:estimate"):
+                v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(
+                    query_states, key_states, pat.vertical_size, pat.slash_size, cap_v=pat.cap_v, cap_s=pat.cap_s)
+            with _cabi.nvtx_range("minference:plan"):
+                plan.v_idx = build_vertical_slash_plan_into(plan, v_idx, s_idx, nnz_v, nnz_s)
         if pat.any_bs:
             q = query_states if query_states.stride(3) == 1 else query_states.contiguous()
             k = key_states if key_states.stride(3) == 1 else key_states.contiguous()
-            build_block_sparse_plan(q, k, BLOCK_SPARSE_TOPK, plan=plan, head_select=pat.block_select)
-    out = sparse_attention_forward(query_states, key_states, value_states, plan,
-                                   head_mode=pat.head_mode, head_param=pat.head_param)
+            with _cabi.nvtx_range("minference:block_plan"):
+                build_block_sparse_plan(q, k, BLOCK_SPARSE_TOPK, plan=plan, head_select=pat.block_select)
+    with _cabi.nvtx_range("minference:attention"):
+        out = sparse_attention_forward(query_states, key_states, value_states, plan,
+                                       head_mode=pat.head_mode, head_param=pat.head_param)
     if _status_checks_enabled():
         _cabi.raise_on_status(plan.status if plan is not None else sparse_attention_forward.last_status,
                               "minference_prefill_forward")

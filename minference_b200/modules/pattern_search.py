@@ -12,9 +12,17 @@ with the base-2 log-sum-exp the forward kernel returns next to its output.  One 
 candidate for every head of the layer; the dense log-sum-exp is one more launch.
 
 The candidates, the order they are tried in, the strict ``>`` that keeps the first best one and
-the two renaming rules at the end (:217-220) are the reference's.  Scores are those of the index
-set the kernels compute (64-wide tiles around each selected diagonal, 64-row blocks), a superset
-of the fine-grained masks the reference scores, so they are never lower than the reference's.
+the two renaming rules at the end (:217-220) are the reference's, and so are the selection rules of
+its vertical-slash candidates: only the 30 nearest diagonals are forced and the budgets are taken as
+they are (:140-146; the online path forces 100 and raises budgets to 30 / 50).
+
+Two deviations remain, both on the side of a candidate's score, not of its lists.  A vertical-slash
+candidate is scored over the index set the kernels compute -- a 64-wide tile around each selected
+diagonal per 64-row block -- which contains the reference's one-token-wide diagonals, so its score
+is never lower than the reference's, while the stream_llm candidate is masked exactly as in the
+reference.  The block-sparse candidate pools 64-token blocks where the reference's search pools 32
+(:178); that candidate is renamed to the default pattern whenever it wins, so only its score differs.
+A searched table can therefore differ from the reference's on heads where two candidates are close.
 """
 from __future__ import annotations
 
@@ -47,10 +55,19 @@ def _dense_lse(q, k, v):
     return sparse_attention_forward(q, k, v, None, head_mode=mode, head_param=param, return_lse=True)[1]
 
 
+def search_vertical_slash_lists(q, k, v_size: int, s_size: int):
+    """Index lists of a vertical-slash candidate under the search's selection rules (:140-146): first 30
+    columns and the 30 nearest diagonals forced, budgets not raised."""
+    from .minference_forward import vertical_slash_estimate, vertical_slash_select
+
+    H, N = q.shape[1], q.shape[2]
+    *_, vsc, ssc = vertical_slash_estimate(q, k, v_size, s_size, return_scores=True)
+    budget = lambda x: torch.full((q.shape[0] * H,), x, dtype=torch.int32, device=q.device)
+    return vertical_slash_select(vsc, ssc, budget(v_size), budget(s_size), min(N, v_size), min(N, s_size), rules="search")
+
+
 def candidate_lse(q, k, v, ty: str, v_size: int, s_size: int):
     """Base-2 log-sum-exp per row under one candidate pattern applied to every head."""
-    from .minference_forward import vertical_slash_estimate
-
     H, N = q.shape[1], q.shape[2]
     dev = q.device
     if ty == "stream_llm":          # sink of v_size keys + window of s_size keys (:166-175)
@@ -58,7 +75,7 @@ def candidate_lse(q, k, v, ty: str, v_size: int, s_size: int):
         param = torch.tensor([[v_size, s_size + 1]] * H, dtype=torch.int32, device=dev)   # i - j <= s_size
         return sparse_attention_forward(q, k, v, None, head_mode=mode, head_param=param, return_lse=True)[1]
     if ty == "vertical_and_slash":
-        v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(q, k, v_size, s_size)
+        v_idx, s_idx, nnz_v, nnz_s = search_vertical_slash_lists(q, k, v_size, s_size)
         plan = build_vertical_slash_plan(v_idx, s_idx, N, nnz_v, nnz_s)
         return sparse_attention_forward(q, k, v, plan, return_lse=True)[1]
     if ty == "block_sparse":        # keep one block in v_size per query block (:177-197)

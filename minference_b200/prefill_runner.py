@@ -68,15 +68,28 @@ class LlamaPrefill:
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, attn_forward_config: dict, chunk: int = 16384,
-                positions: torch.Tensor | None = None, attention=None) -> torch.Tensor:
+                positions: torch.Tensor | None = None, attention=None, timing: dict | None = None) -> torch.Tensor:
         """``ids [N]`` (this rank's tokens) -> fp32 logits ``[vocab]`` of the last local token.
 
         ``positions [N]`` are the tokens' positions in the whole prompt (default 0..N-1).
         ``attention(q, k, v, layer_idx)`` replaces the single-GPU operator (the ring passes one).
+        ``timing``: a dict that receives CUDA-event pairs, ``"gemm"`` around every projection / MLP product and
+        ``"attention"`` around every layer's attention (see ``split_times``).
         """
         s = self.shape
         n = ids.numel()
         dev, dt = self.device, self.dtype
+
+        def timed(kind, fn):
+            if timing is None:
+                return fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            timing.setdefault(kind, []).append((e0, e1))
+            return r
+
         x = self.embed[ids.to(dev)]                                   # [N, hidden]
         q = torch.empty(1, s.q_heads, n, s.head_dim, device=dev, dtype=dt)
         k = torch.empty(1, s.kv_heads, n, s.head_dim, device=dev, dtype=dt)
@@ -85,7 +98,8 @@ class LlamaPrefill:
         for li, L in enumerate(self.layers):
             for c0 in range(0, n, chunk):
                 c1 = min(c0 + chunk, n)
-                qkv = self._rms(x[c0:c1], L["attn_norm"]) @ L["wqkv"]
+                h_in = self._rms(x[c0:c1], L["attn_norm"])
+                qkv = timed("gemm", lambda: h_in @ L["wqkv"])
                 if positions is None:
                     cos, sin = rope_cos_sin(c1 - c0, s.head_dim, s.rope_theta, dev, start=c0)
                 else:
@@ -97,18 +111,30 @@ class LlamaPrefill:
                 k[0, :, c0:c1] = kc.transpose(0, 1)
                 v[0, :, c0:c1] = qkv[:, nq + nk:].view(c1 - c0, s.kv_heads, s.head_dim).transpose(0, 1)
             if attention is not None:
-                o = attention(q, k, v, li)
+                o = timed("attention", lambda: attention(q, k, v, li))
             else:
-                o = minference_prefill_forward(q, k, v, {"attention_mask": None, "layer_idx": li,
-                                                         "num_hidden_layers": s.layers,
-                                                         "attn_forward_config": attn_forward_config})
+                o = timed("attention", lambda: minference_prefill_forward(
+                    q, k, v, {"attention_mask": None, "layer_idx": li, "num_hidden_layers": s.layers,
+                              "attn_forward_config": attn_forward_config}))
             for c0 in range(0, n, chunk):
                 c1 = min(c0 + chunk, n)
-                x[c0:c1] += o[0, :, c0:c1].transpose(0, 1).reshape(c1 - c0, nq) @ L["wo"]
-                gu = self._rms(x[c0:c1], L["mlp_norm"]) @ L["w_gate_up"]
-                x[c0:c1] += (torch.nn.functional.silu(gu[:, :s.ffn]) * gu[:, s.ffn:]) @ L["w_down"]
+                o_rows = o[0, :, c0:c1].transpose(0, 1).reshape(c1 - c0, nq)
+                x[c0:c1] += timed("gemm", lambda: o_rows @ L["wo"])
+                h_mlp = self._rms(x[c0:c1], L["mlp_norm"])
+                gu = timed("gemm", lambda: h_mlp @ L["w_gate_up"])
+                act = torch.nn.functional.silu(gu[:, :s.ffn]) * gu[:, s.ffn:]
+                x[c0:c1] += timed("gemm", lambda: act @ L["w_down"])
             del o
         return (self._rms(x[-1:], self.final_norm) @ self.lm_head)[0].float()
+
+
+def split_times(timing: dict, total_ms: float, layers: int) -> dict:
+    """Milliseconds per layer of attention, of the dense products and of everything else (norms, rotary embedding,
+    activation, residual adds, copies) from the event pairs ``prefill(timing=...)`` recorded; synchronise first."""
+    gemm = sum(a.elapsed_time(b) for a, b in timing.get("gemm", []))
+    attn = sum(a.elapsed_time(b) for a, b in timing.get("attention", []))
+    return {"attention_ms_per_layer": attn / layers, "dense_gemm_ms_per_layer": gemm / layers,
+            "rest_ms_per_layer": max(total_ms - gemm - attn, 0.0) / layers}
 
 
 def zigzag_positions(n_ctx: int, rank: int, world: int, device=None) -> torch.Tensor:

@@ -8,8 +8,7 @@ pytestmark = pytest.mark.gpu
 
 
 def test_search_scores_match_attention_mass_of_the_masks():
-    from minference_b200.modules.minference_forward import vertical_slash_estimate
-    from minference_b200.modules.pattern_search import CANDIDATES, search_layer_patterns
+    from minference_b200.modules.pattern_search import CANDIDATES, search_layer_patterns, search_vertical_slash_lists
     from minference_b200.ops.block_sparse_flash_attention import _build_block_index, _rows_pad
     from minference_b200.synthetic import make_qkv
     from oracle import reference_math as R
@@ -31,7 +30,11 @@ def test_search_scores_match_attention_mass_of_the_masks():
             if ty == "stream_llm":
                 mask = R.a_shape_mask_rows(n, vs, ss + 1, 0, n)
             elif ty == "vertical_and_slash":
-                v_idx, s_idx, nnz_v, nnz_s = vertical_slash_estimate(dq, dk, vs, ss)
+                v_idx, s_idx, nnz_v, nnz_s = search_vertical_slash_lists(dq, dk, vs, ss)
+                assert int(nnz_v[h]) == min(n, vs) and int(nnz_s[h]) == min(n, ss)       # budgets as given, not raised
+                assert set(range(30)) <= set(s_idx[0, h, : int(nnz_s[h])].tolist())         # the 30 nearest diagonals, not 100
+                if ss == 100:
+                    assert not set(range(100)) <= set(s_idx[0, h, :100].tolist())
                 bc, bo, cc, ci = R.convert_vertical_slash_indexes(
                     np.array([n], np.int32), v_idx[:, h:h + 1, : int(nnz_v[h])].cpu().numpy(),
                     s_idx[:, h:h + 1, : int(nnz_s[h])].cpu().numpy(), n)
