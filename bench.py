@@ -330,10 +330,9 @@ def side_measurement(name, dev, steps=2, warmup=1):
     if st[0] or st[1]:
         raise SystemExit(f"{name}: device status {st}")
     tiles = plan.count_tiles()
-    plan.status[2:].zero_()
     step(False)
     torch.cuda.synchronize()
-    issued = issued_tiles_of(plan.status)
+    issued = issued_tiles_of(box["plan"].status)          # the plan (and status words) of that one step
     attn_ms = sum(a.elapsed_time(b) for a, b in events["attn"]) / steps
     peaks = measured_peaks()
     rows = (n + 63) // 64

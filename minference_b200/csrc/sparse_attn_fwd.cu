@@ -45,7 +45,13 @@
 namespace minf {
 
 constexpr int kHeadDim = 128;
-constexpr int kNK = 2, kNV = 3, kNM = 8;           // K stages, V stages, step-descriptor ring
+#ifndef MINF_NK
+#define MINF_NK 2
+#endif
+#ifndef MINF_NV
+#define MINF_NV 3
+#endif
+constexpr int kNK = MINF_NK, kNV = MINF_NV, kNM = 8;   // K stages, V stages, step-descriptor ring
 constexpr uint32_t kTile = 128 * 256;              // 128 rows x 128 bf16
 constexpr uint32_t kQOff = 0;
 constexpr uint32_t kKOff = 2 * kTile;
@@ -663,10 +669,18 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 // A slot that sits out this step has a free S: its next QK^T goes first, so that its
                 // softmax runs while this step's P is still being made (steps of scattered diagonals
                 // touch one slot each, alternating).
+#ifdef MINF_NO_EARLY_QK
+                const int early = 0;
+#else
                 const int early = nxt_live ? (nxt.w & ~cur.w) : 0;
+#endif
 #pragma unroll
                 for (int s = 0; s < 2; ++s)
                     if ((early >> s) & 1) issue_s(j + 1, s, nxt.z);
+                // when every slot of the next step went early, its K stage is released now, not after this
+                // step's P has arrived: the producer needs that head start to hide the load of the stage's next tile
+                const bool k_released = early != 0 && (nxt.w & ~early) == 0;
+                if (k_released && elect_one()) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
                 ok = wait(&ctl->v_full[kv], kv_par);
                 if (!ok) break;
 #pragma unroll
@@ -686,7 +700,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!ok) break;
                 if (elect_one()) {
                     umma_commit(bar(&ctl->v_empty[kv]));
-                    if (nxt_live) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
+                    if (nxt_live && !k_released) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
                     mbar_arrive(bar(&ctl->m_empty[j % kNM]));
                 }
                 cur = nxt;

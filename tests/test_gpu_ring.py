@@ -16,11 +16,17 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _one_rounding_apart(a, b):
-    """bf16 results of two fp32 computations that differ by summation order: equal or adjacent bf16 values."""
+def _one_rounding_apart(a, b, slack: float = 2e-3):
+    """Two bf16 results of the same attention computed through different chains of key chunks.  Both accumulate in
+    fp32 and round the output once, but P is rounded to bf16 against each chain's own running maximum, which moves
+    the fp32 sums by a few 1e-4 of their terms: the results are equal or neighbouring bf16 values, up to `slack` for
+    outputs that are small because their terms cancel."""
     a, b = a.float(), b.float()
     ulp = torch.exp2(torch.floor(torch.log2(torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -100))) - 7)
-    return bool(((a - b).abs() <= ulp * 1.001 + 1e-30).all())
+    excess = ((a - b).abs() - ulp * 1.001 - slack).max().item()
+    if excess > 0:
+        print(f"largest difference beyond one bf16 step + {slack}: {excess:.3e}; max abs difference {(a - b).abs().max().item():.3e}")
+    return excess <= 0
 
 
 def _pairs_through_carry(ring, qs, ks, vs, n, c, qc, plan, v_idx, cap_s, status, world, **kw):
