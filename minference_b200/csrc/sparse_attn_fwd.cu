@@ -4,15 +4,17 @@
 // One CTA owns 256 consecutive query rows of one head (4 row blocks of 64, the granularity at
 // which the reference defines its index set, ops/pit_sparse_flash_attention_v2.py:64-153) as two
 // 128-row slots.  Warp roles (three warpgroups of four warps):
-//   warp 0          producer: merges the plans of the four row blocks into one stream of steps.
+//   warp 0          planner: merges the plans of the four row blocks into one stream of steps.
 //                   A step is 64 or 128 keys -- a contiguous token range (TMA) or gathered
-//                   vertical columns (cp.async) -- with a 128-bit key mask per row block.
-//                   K and V travel through separate rings so a K stage is recycled as soon as
-//                   both QK^T products have read it.
+//                   vertical columns (cp.async) -- with a 128-bit key mask per row block, published
+//                   through an eight-deep descriptor ring; the planner also fills the gather steps.
+//   warp 2          loader: follows the descriptor ring and issues the TMA loads of the contiguous
+//                   steps.  K and V travel through separate rings so a K stage is recycled as soon
+//                   as both QK^T products have read it.
 //   warp 1          issues every tcgen05.mma and tcgen05.commit (the whole warp follows the control
 //                   flow, one lane elected per instruction) and owns the TMEM allocation
-//   warps 2-3       spare (they keep the roles aligned to warpgroups of four; setmaxnreg hands
-//                   their registers to the softmax warps)
+//   warp 3          spare (keeps the roles aligned to warpgroups of four; setmaxnreg hands the
+//                   registers of warps 0-3 to the softmax warps)
 //   warps 4-7/8-11  softmax of slot 0 / slot 1, one thread per query row, the whole 128-key row
 //                   of S in registers
 // TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written back
@@ -286,7 +288,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         mbar_init(bar(&ctl->q_full), 1);
         for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 1); mbar_init(bar(&ctl->k_empty[s]), 1); }
         for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 1); mbar_init(bar(&ctl->v_empty[s]), 1); }
-        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA lane + 8 softmax warps
+        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 10); }   // MMA lane, loader lane, 8 softmax warps
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(&ctl->s_full[s]), 1);
             mbar_init(bar(&ctl->p_half[s][0]), 128);
@@ -341,30 +343,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             }
             return true;
         };
-        auto load_tile = [&](int t, int width) -> bool {     // t: global position, inside the local key window
-            const int lt = t - a.kv_pos0;
-            if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) return true;      // a tile that starts outside the local keys
-            if (!wait_use(ctl->k_empty, kNK, step)) return false;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
-                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
-            }
-            if (!wait_use(ctl->v_empty, kNV, step)) return false;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
-                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
-            }
-            return true;
-        };
-
         if (mode == MINF_MODE_ASHAPE) {
             const int r_hi = min(row0 + 256, a.q_pos0 + a.n_q) - 1;
             int w0 = row0 - n_local + 1;
@@ -389,7 +367,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         mk[r][1] = sees ? ~0ull : 0ull;
                     }
                     if (!publish(kTileStep, t, width, mk)) break;
-                    if (!load_tile(t, width)) break;
                     ++step;
                     t += width;
                 }
@@ -471,7 +448,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
                 const int width = any_hi ? 128 : 64;
                 if (!publish(kTileStep, t, width, mk)) break;
-                if (!load_tile(t, width)) break;
                 ++step;
             }
 #pragma unroll
@@ -713,7 +689,48 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 umma_commit(bar(&ctl->o_done[1]));
             }
         }
-    } else if (warp < 4) {
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ loader
+        // Follows the planner through the descriptor ring and issues the TMA loads of the contiguous-tile
+        // steps, so that merging the row blocks' plans (warp 0) never waits for a free K/V stage and the
+        // loads never wait for the merge of the next step.  Gather steps are filled by the planner itself.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        bool ok = true;
+        auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
+            const int s = idx % ring, use = idx / ring;
+            if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
+            return true;
+        };
+        for (int step = 0; ok; ++step) {
+            ok = mbar_wait(bar(&ctl->m_full[step % kNM]), (step / kNM) & 1, abort_flag);
+            if (!ok) break;
+            const int4 d = *reinterpret_cast<const int4*>(&ctl->step[step % kNM]);     // kind, first key, width, live slots
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(&ctl->m_empty[step % kNM]));
+            if (d.x == kEndStep) break;
+            if (d.x != kTileStep) continue;
+            const int lt = d.y - a.kv_pos0, width = d.z;      // inside the local key window
+            if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) continue;
+            if (!wait_use(ctl->k_empty, kNK, step)) break;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+            if (!wait_use(ctl->v_empty, kNV, step)) break;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+        }
+    } else if (warp == 3) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     } else {
         // ------------------------------------------------------------------ softmax / epilogue

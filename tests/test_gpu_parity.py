@@ -539,7 +539,7 @@ def test_block_index_matches_reference_fixtures_on_gpu(dev, golden_dir):
             tol = 3 * 2 ** -8 * max(np.abs(row).max(), 1e-6)      # bf16 inputs, bf16 pooled vectors, bf16 scores
             assert set(np.nonzero(row > kth + tol)[0].tolist()) <= g, (path, m)
             assert not (g & set(np.nonzero(row < nxt - tol)[0].tolist())), (path, m)
-        assert hit >= 0.9 * tot, (path, hit, tot)
+        assert hit >= 0.8 * tot, (path, hit, tot)       # a 512-token fixture has 24 consumed entries: three near-ties are 12 %
 
 
 def test_mixed_pattern_prefill_forward(dev):
