@@ -77,6 +77,7 @@ struct Control {
     unsigned long long s_full[2], p_half[2][2], o_done[2];   // P is published in two halves per step
     uint32_t tmem_base;
     int abort;
+    int loader_pos;      // number of steps the loader warp has dealt with (written by its lane 0)
     Step step[kNM];
     int colring[256];
 };
@@ -296,6 +297,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             mbar_init(bar(&ctl->o_done[s]), 1);
         }
         ctl->abort = 0;
+        ctl->loader_pos = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -327,6 +329,20 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             const int s = idx % ring, use = idx / ring;
             if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
             return true;
+        };
+        // The planner runs up to eight steps ahead of the loader.  Before it fills a K/V stage itself (gather
+        // steps, the end marker) the loader must have dealt with every earlier step: a parity wait on a stage
+        // barrier is only meaningful for a waiter that is at most one phase ahead of it.
+        auto wait_loader = [&](int upto) -> bool {
+            const volatile int* pos = &ctl->loader_pos;
+            if (*pos >= upto) return true;
+            const uint64_t t0 = global_timer_ns();
+            for (;;) {
+                __nanosleep(100);
+                if (*pos >= upto) return true;
+                if (*abort_flag) { ok = false; return false; }
+                if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; ok = false; return false; }
+            }
         };
         auto publish = [&](int kind, int t, int width, const unsigned long long (&mk)[4][2]) -> bool {
             if (!wait_use(ctl->m_empty, kNM, step)) return false;
@@ -477,6 +493,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     mk[r][1] = (unsigned long long)bl[2] | ((unsigned long long)bl[3] << 32);
                 }
                 if (!publish(kGatherStep, 0, width, mk)) return;
+                if (!wait_loader(step)) return;
                 int col[4];      // local key rows
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -556,7 +573,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             // the end marker travels like a step: the MMA warp reads a step's descriptor once the
             // step's K stage is full, so the marker completes a K stage too (with no load)
             const unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
-            if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
+            if (publish(kEndStep, 0, 0, none) && wait_loader(step) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
                 mbar_arrive(bar(&ctl->k_full[step % kNK]));
         }
         if (lane == 0 && bad_plan) atomicOr(a.status + MINF_ST_ERROR, 4);
@@ -708,26 +725,30 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(&ctl->m_empty[step % kNM]));
             if (d.x == kEndStep) break;
-            if (d.x != kTileStep) continue;
-            const int lt = d.y - a.kv_pos0, width = d.z;      // inside the local key window
-            if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) continue;
-            if (!wait_use(ctl->k_empty, kNK, step)) break;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
-                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            if (d.x == kTileStep) {               // gather steps are the planner's
+                const int lt = d.y - a.kv_pos0, width = d.z;      // inside the local key window
+                if (!wait_use(ctl->k_empty, kNK, step)) break;
+                if (lane == 0) {
+                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                    const uint32_t fb = bar(&ctl->k_full[step % kNK]);
+                    mbar_arrive_expect_tx(fb, width * 256);
+                    const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                }
+                if (!wait_use(ctl->v_empty, kNV, step)) break;
+                if (lane == 0) {
+                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                    const uint32_t fb = bar(&ctl->v_full[step % kNV]);
+                    mbar_arrive_expect_tx(fb, width * 256);
+                    const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                }
             }
-            if (!wait_use(ctl->v_empty, kNV, step)) break;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
-                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            if (lane == 0) {                      // this step is dealt with as far as the loader goes
+                __threadfence_block();
+                *(volatile int*)&ctl->loader_pos = step + 1;
             }
         }
     } else if (warp == 3) {
@@ -864,7 +885,13 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
 
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && ctl->abort) atomicOr(a.status + MINF_ST_ERROR, 1);
+    if (ctl->abort) {
+        // a wait was abandoned: give the copies and products this CTA may still have in flight time to land
+        // before its shared memory and TMEM go to the next CTA
+        __nanosleep(50000);
+        if (threadIdx.x == 0) atomicOr(a.status + MINF_ST_ERROR, 1);
+    }
+    __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
