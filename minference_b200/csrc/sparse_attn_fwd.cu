@@ -4,17 +4,15 @@
 // One CTA owns 256 consecutive query rows of one head (4 row blocks of 64, the granularity at
 // which the reference defines its index set, ops/pit_sparse_flash_attention_v2.py:64-153) as two
 // 128-row slots.  Warp roles (three warpgroups of four warps):
-//   warp 0          planner: merges the plans of the four row blocks into one stream of steps.
+//   warp 0          producer: merges the plans of the four row blocks into one stream of steps.
 //                   A step is 64 or 128 keys -- a contiguous token range (TMA) or gathered
-//                   vertical columns (cp.async) -- with a 128-bit key mask per row block, published
-//                   through an eight-deep descriptor ring; the planner also fills the gather steps.
-//   warp 2          loader: follows the descriptor ring and issues the TMA loads of the contiguous
-//                   steps.  K and V travel through separate rings so a K stage is recycled as soon
-//                   as both QK^T products have read it.
+//                   vertical columns (cp.async) -- with a 128-bit key mask per row block.
+//                   K and V travel through separate rings so a K stage is recycled as soon as
+//                   both QK^T products have read it.
 //   warp 1          issues every tcgen05.mma and tcgen05.commit (the whole warp follows the control
 //                   flow, one lane elected per instruction) and owns the TMEM allocation
-//   warp 3          spare (keeps the roles aligned to warpgroups of four; setmaxnreg hands the
-//                   registers of warps 0-3 to the softmax warps)
+//   warps 2-3       spare (they keep the roles aligned to warpgroups of four; setmaxnreg hands
+//                   their registers to the softmax warps)
 //   warps 4-7/8-11  softmax of slot 0 / slot 1, one thread per query row, the whole 128-key row
 //                   of S in registers
 // TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written back
@@ -47,13 +45,7 @@
 namespace minf {
 
 constexpr int kHeadDim = 128;
-#ifndef MINF_NK
-#define MINF_NK 2
-#endif
-#ifndef MINF_NV
-#define MINF_NV 3
-#endif
-constexpr int kNK = MINF_NK, kNV = MINF_NV, kNM = 8;   // K stages, V stages, step-descriptor ring
+constexpr int kNK = 2, kNV = 3, kNM = 8;           // K stages, V stages, step-descriptor ring
 constexpr uint32_t kTile = 128 * 256;              // 128 rows x 128 bf16
 constexpr uint32_t kQOff = 0;
 constexpr uint32_t kKOff = 2 * kTile;
@@ -77,7 +69,6 @@ struct Control {
     unsigned long long s_full[2], p_half[2][2], o_done[2];   // P is published in two halves per step
     uint32_t tmem_base;
     int abort;
-    int loader_pos;      // number of steps the loader warp has dealt with (written by its lane 0)
     Step step[kNM];
     int colring[256];
 };
@@ -289,7 +280,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
         mbar_init(bar(&ctl->q_full), 1);
         for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 1); mbar_init(bar(&ctl->k_empty[s]), 1); }
         for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 1); mbar_init(bar(&ctl->v_empty[s]), 1); }
-        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 10); }   // MMA lane, loader lane, 8 softmax warps
+        for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA lane + 8 softmax warps
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(&ctl->s_full[s]), 1);
             mbar_init(bar(&ctl->p_half[s][0]), 128);
@@ -297,7 +288,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             mbar_init(bar(&ctl->o_done[s]), 1);
         }
         ctl->abort = 0;
-        ctl->loader_pos = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -330,20 +320,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
             return true;
         };
-        // The planner runs up to eight steps ahead of the loader.  Before it fills a K/V stage itself (gather
-        // steps, the end marker) the loader must have dealt with every earlier step: a parity wait on a stage
-        // barrier is only meaningful for a waiter that is at most one phase ahead of it.
-        auto wait_loader = [&](int upto) -> bool {
-            const volatile int* pos = &ctl->loader_pos;
-            if (*pos >= upto) return true;
-            const uint64_t t0 = global_timer_ns();
-            for (;;) {
-                __nanosleep(100);
-                if (*pos >= upto) return true;
-                if (*abort_flag) { ok = false; return false; }
-                if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; ok = false; return false; }
-            }
-        };
         auto publish = [&](int kind, int t, int width, const unsigned long long (&mk)[4][2]) -> bool {
             if (!wait_use(ctl->m_empty, kNM, step)) return false;
             if (lane == 0) {
@@ -359,6 +335,30 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             }
             return true;
         };
+        auto load_tile = [&](int t, int width) -> bool {     // t: global position, inside the local key window
+            const int lt = t - a.kv_pos0;
+            if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) return true;      // a tile that starts outside the local keys
+            if (!wait_use(ctl->k_empty, kNK, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                const uint32_t fb = bar(&ctl->k_full[step % kNK]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+            if (!wait_use(ctl->v_empty, kNV, step)) return false;
+            if (lane == 0) {
+                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                const uint32_t fb = bar(&ctl->v_full[step % kNV]);
+                mbar_arrive_expect_tx(fb, width * 256);
+                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+            }
+            return true;
+        };
+
         if (mode == MINF_MODE_ASHAPE) {
             const int r_hi = min(row0 + 256, a.q_pos0 + a.n_q) - 1;
             int w0 = row0 - n_local + 1;
@@ -383,6 +383,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         mk[r][1] = sees ? ~0ull : 0ull;
                     }
                     if (!publish(kTileStep, t, width, mk)) break;
+                    if (!load_tile(t, width)) break;
                     ++step;
                     t += width;
                 }
@@ -464,6 +465,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 }
                 const int width = any_hi ? 128 : 64;
                 if (!publish(kTileStep, t, width, mk)) break;
+                if (!load_tile(t, width)) break;
                 ++step;
             }
 #pragma unroll
@@ -493,7 +495,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     mk[r][1] = (unsigned long long)bl[2] | ((unsigned long long)bl[3] << 32);
                 }
                 if (!publish(kGatherStep, 0, width, mk)) return;
-                if (!wait_loader(step)) return;
                 int col[4];      // local key rows
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -573,7 +574,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             // the end marker travels like a step: the MMA warp reads a step's descriptor once the
             // step's K stage is full, so the marker completes a K stage too (with no load)
             const unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
-            if (publish(kEndStep, 0, 0, none) && wait_loader(step) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
+            if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
                 mbar_arrive(bar(&ctl->k_full[step % kNK]));
         }
         if (lane == 0 && bad_plan) atomicOr(a.status + MINF_ST_ERROR, 4);
@@ -659,21 +660,6 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 if (!ok) break;
                 const int4 nxt = read_step(j + 1);
                 const bool nxt_live = nxt.x != kEndStep;
-                // A slot that sits out this step has a free S: its next QK^T goes first, so that its
-                // softmax runs while this step's P is still being made (steps of scattered diagonals
-                // touch one slot each, alternating).
-#ifdef MINF_NO_EARLY_QK
-                const int early = 0;
-#else
-                const int early = nxt_live ? (nxt.w & ~cur.w) : 0;
-#endif
-#pragma unroll
-                for (int s = 0; s < 2; ++s)
-                    if ((early >> s) & 1) issue_s(j + 1, s, nxt.z);
-                // when every slot of the next step went early, its K stage is released now, not after this
-                // step's P has arrived: the producer needs that head start to hide the load of the stage's next tile
-                const bool k_released = early != 0 && (nxt.w & ~early) == 0;
-                if (k_released && elect_one()) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
                 ok = wait(&ctl->v_full[kv], kv_par);
                 if (!ok) break;
 #pragma unroll
@@ -688,12 +674,12 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         tc_fence_after();
                         issue_pv_half(j, kv, s, cur.z, 1);
                     }
-                    if (nxt_live && ((nxt.w & ~early) >> s) & 1) issue_s(j + 1, s, nxt.z);
+                    if (nxt_live && ((nxt.w >> s) & 1)) issue_s(j + 1, s, nxt.z);
                 }
                 if (!ok) break;
                 if (elect_one()) {
                     umma_commit(bar(&ctl->v_empty[kv]));
-                    if (nxt_live && !k_released) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
+                    if (nxt_live) umma_commit(bar(&ctl->k_empty[(j + 1) % kNK]));
                     mbar_arrive(bar(&ctl->m_empty[j % kNM]));
                 }
                 cur = nxt;
@@ -706,52 +692,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 umma_commit(bar(&ctl->o_done[1]));
             }
         }
-    } else if (warp == 2) {
-        // ------------------------------------------------------------------ loader
-        // Follows the planner through the descriptor ring and issues the TMA loads of the contiguous-tile
-        // steps, so that merging the row blocks' plans (warp 0) never waits for a free K/V stage and the
-        // loads never wait for the merge of the next step.  Gather steps are filled by the planner itself.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-        bool ok = true;
-        auto wait_use = [&](unsigned long long* bars, int ring, int idx) -> bool {
-            const int s = idx % ring, use = idx / ring;
-            if (use > 0 && !mbar_wait(bar(&bars[s]), (use - 1) & 1, abort_flag)) { ok = false; return false; }
-            return true;
-        };
-        for (int step = 0; ok; ++step) {
-            ok = mbar_wait(bar(&ctl->m_full[step % kNM]), (step / kNM) & 1, abort_flag);
-            if (!ok) break;
-            const int4 d = *reinterpret_cast<const int4*>(&ctl->step[step % kNM]);     // kind, first key, width, live slots
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(&ctl->m_empty[step % kNM]));
-            if (d.x == kEndStep) break;
-            if (d.x == kTileStep) {               // gather steps are the planner's
-                const int lt = d.y - a.kv_pos0, width = d.z;      // inside the local key window
-                if (!wait_use(ctl->k_empty, kNK, step)) break;
-                if (lane == 0) {
-                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
-                    const uint32_t fb = bar(&ctl->k_full[step % kNK]);
-                    mbar_arrive_expect_tx(fb, width * 256);
-                    const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
-                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
-                }
-                if (!wait_use(ctl->v_empty, kNV, step)) break;
-                if (lane == 0) {
-                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
-                    const uint32_t fb = bar(&ctl->v_full[step % kNV]);
-                    mbar_arrive_expect_tx(fb, width * 256);
-                    const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
-                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
-                }
-            }
-            if (lane == 0) {                      // this step is dealt with as far as the loader goes
-                __threadfence_block();
-                *(volatile int*)&ctl->loader_pos = step + 1;
-            }
-        }
-    } else if (warp == 3) {
+    } else if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
