@@ -156,14 +156,15 @@ __device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigne
 
 // One softmax step of one query row: S (fp32, NCH*32 columns at t_s) -> P (bf16 pairs written
 // back over the first NCH*16 columns).  The whole row is held in registers, so TMEM is read
-// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.  SKIP: a 64-key half that no row
-// of the warp can see (the other row block's half of an isolated diagonal, keys past the causal
-// limit; live0 / live1 are warp-uniform) is not exponentiated: its P is written as zeros.
-template <int NCH, bool SKIP>
+// once.  m0/m1 hold the visibility bits of keys 0-63 / 64-127.
+// (Skipping the exponentials of a 32- or 64-key part that no row of the warp can see -- the other row
+// block's half of an isolated diagonal -- was built and measured in two forms: it changed nothing on
+// scattered index sets, whose steps are bound by the softmax -> PV -> QK^T chain of a slot and not by the
+// MUFU, and it cost 4 % on dense ones, so every chunk is processed.)
+template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,
-                                            uint32_t bar_half0, uint32_t bar_half1, bool live0, bool live1) {
-    auto chunk_live = [&](int c) { return !SKIP || (c < NCH / 2 ? live0 : live1); };   // the halves P is published in
+                                            uint32_t bar_half0, uint32_t bar_half1) {
     // The row maximum of a chunk is taken while the next chunk's load is in flight.
     uint32_t sr[NCH][32];
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -172,17 +173,15 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
     for (int c = 0; c < NCH; ++c) {
         tmem_wait_ld();
         if (c + 1 < NCH) tmem_ld32(t_s + 32 * (c + 1), sr[c + 1]);
-        if (chunk_live(c)) {
-            const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
-            if (cm != 0xffffffffu) {
+        const uint32_t cm = (uint32_t)((c < 2 ? m0 : m1) >> (32 * (c & 1)));
+        if (cm != 0xffffffffu) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 2)
-                mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+            for (int i = 0; i < 32; ++i)
+                if (!((cm >> i) & 1u)) sr[c][i] = 0xff800000u;   // -inf
         }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
     }
     const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
     float alpha = 1.f;
@@ -212,18 +211,13 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
         uint32_t pk[16];
-        if (chunk_live(c)) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float x0, x1;
-                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2), x0, x1);
-                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                ps2[(i >> 1) & 3] = add_f32x2(ps2[(i >> 1) & 3], pack_f32x2(p0, p1));
-                pk[i >> 1] = pack_bf16x2(p0, p1);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = 0u;
+        for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2), x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            ps2[(i >> 1) & 3] = add_f32x2(ps2[(i >> 1) & 3], pack_f32x2(p0, p1));
+            pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st16(t_s + 16 * c, pk);
         if (c == NCH / 2 - 1) {
@@ -278,8 +272,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
 
     if (threadIdx.x == 0) {
         mbar_init(bar(&ctl->q_full), 1);
-        for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 1); mbar_init(bar(&ctl->k_empty[s]), 1); }
-        for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 1); mbar_init(bar(&ctl->v_empty[s]), 1); }
+        // a stage is full when all 32 producer lanes have arrived: at once for a TMA tile (lane 0 adds the byte
+        // count), each lane as its own copies land for a gathered one
+        for (int s = 0; s < kNK; ++s) { mbar_init(bar(&ctl->k_full[s]), 32); mbar_init(bar(&ctl->k_empty[s]), 1); }
+        for (int s = 0; s < kNV; ++s) { mbar_init(bar(&ctl->v_full[s]), 32); mbar_init(bar(&ctl->v_empty[s]), 1); }
         for (int s = 0; s < kNM; ++s) { mbar_init(bar(&ctl->m_full[s]), 1); mbar_init(bar(&ctl->m_empty[s]), 9); }   // MMA lane + 8 softmax warps
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar(&ctl->s_full[s]), 1);
@@ -339,22 +335,30 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             const int lt = t - a.kv_pos0;
             if (!MINF_IN_BOUNDS(a.status, lt >= 0 && lt < a.n_kv)) return true;      // a tile that starts outside the local keys
             if (!wait_use(ctl->k_empty, kNK, step)) return false;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+            {
                 const uint32_t fb = bar(&ctl->k_full[step % kNK]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                if (lane == 0) {
+                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
+                    mbar_arrive_expect_tx(fb, width * 256);
+                    const CUtensorMap* m = width == 128 ? &tm.k128 : &tm.k64;
+                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                } else {
+                    mbar_arrive(fb);
+                }
             }
             if (!wait_use(ctl->v_empty, kNV, step)) return false;
-            if (lane == 0) {
-                const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+            {
                 const uint32_t fb = bar(&ctl->v_full[step % kNV]);
-                mbar_arrive_expect_tx(fb, width * 256);
-                const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
-                tma_load_4d(dst, m, fb, 0, lt, hk, b);
-                tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                if (lane == 0) {
+                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
+                    mbar_arrive_expect_tx(fb, width * 256);
+                    const CUtensorMap* m = width == 128 ? &tm.v128 : &tm.v64;
+                    tma_load_4d(dst, m, fb, 0, lt, hk, b);
+                    tma_load_4d(dst + 16384, m, fb, 64, lt, hk, b);
+                } else {
+                    mbar_arrive(fb);
+                }
             }
             return true;
         };
@@ -515,9 +519,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
                         cp_async_16(dst + off, kb + (long long)c * a.k_sn + chunk * 8);
                     }
-                    cp_async_commit();
+                    cp_async_arrive_noinc(bar(&ctl->k_full[step % kNK]));      // this lane's K rows, whenever they land
                 }
-                if (!wait_use(ctl->v_empty, kNV, step)) { cp_async_wait<0>(); return; }
+                if (!wait_use(ctl->v_empty, kNV, step)) return;
                 {
                     const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
                     const __nv_bfloat16* vb = a.v + b * a.v_sb + hk * a.v_sh;
@@ -529,16 +533,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                         const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
                         cp_async_16(dst + off, vb + (long long)c * a.v_sn + chunk * 8);
                     }
-                    cp_async_commit();
+                    cp_async_arrive_noinc(bar(&ctl->v_full[step % kNV]));      // ... and its V rows (the planner does not wait)
                 }
-                cp_async_wait<1>();            // K rows landed
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(&ctl->k_full[step % kNK]));
-                cp_async_wait<0>();            // V rows landed
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(&ctl->v_full[step % kNV]));
                 emitted += count;
                 ++step;
             };
@@ -574,8 +570,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             // the end marker travels like a step: the MMA warp reads a step's descriptor once the
             // step's K stage is full, so the marker completes a K stage too (with no load)
             const unsigned long long none[4][2] = {{0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}, {0ull, 0ull}};
-            if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step) && lane == 0)
-                mbar_arrive(bar(&ctl->k_full[step % kNK]));
+            if (publish(kEndStep, 0, 0, none) && wait_use(ctl->k_empty, kNK, step))
+                mbar_arrive(bar(&ctl->k_full[step % kNK]));          // all 32 lanes
         }
         if (lane == 0 && bad_plan) atomicOr(a.status + MINF_ST_ERROR, 4);
         if (lane == 0 && issued)
@@ -647,6 +643,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             int4 cur = make_int4(kEndStep, 0, 0, 0);
             if (ok) ok = wait(&ctl->k_full[0], 0);
             if (ok) {
+                fence_proxy_async_smem();      // rows gathered with cp.async were written through the generic proxy
                 cur = read_step(0);
                 if (cur.x != kEndStep) {
 #pragma unroll
@@ -662,6 +659,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 const bool nxt_live = nxt.x != kEndStep;
                 ok = wait(&ctl->v_full[kv], kv_par);
                 if (!ok) break;
+                fence_proxy_async_smem();      // gathered stages: generic-proxy writes before the tensor pipe reads them
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
                     if ((cur.w >> s) & 1) {
@@ -742,16 +740,10 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             ok = mbar_wait(bar(&ctl->s_full[slot]), n & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            // which halves of the step's keys can some row of this warp see?  (warp-uniform)
-            if (width == 128) {
-                const bool live0 = __any_sync(0xffffffffu, m0 != 0ull), live1 = __any_sync(0xffffffffu, m1 != 0ull);
-                if (live0 && live1)
-                    softmax_row<4, false>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), true, true);
-                else
-                    softmax_row<4, true>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), live0, live1);
-            } else {
-                softmax_row<2, false>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]), true, true);
-            }
+            if (width == 128)
+                softmax_row<4>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
+            else
+                softmax_row<2>(t_s, t_o, m0, m1, a.scale_log2, n > 0, m_ref, l_sum, bar(&ctl->p_half[slot][0]), bar(&ctl->p_half[slot][1]));
             ++n;
         }
 
