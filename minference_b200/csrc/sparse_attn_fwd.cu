@@ -11,8 +11,9 @@
 //                   both QK^T products have read it.
 //   warp 1          issues every tcgen05.mma and tcgen05.commit (the whole warp follows the control
 //                   flow, one lane elected per instruction) and owns the TMEM allocation
-//   warps 2-3       spare (they keep the roles aligned to warpgroups of four; setmaxnreg hands
-//                   their registers to the softmax warps)
+//   warp 2          copies the V rows of gathered steps (the producer copies their K rows)
+//   warp 3          spare (keeps the roles aligned to warpgroups of four; setmaxnreg hands the
+//                   registers of warps 0-3 to the softmax warps)
 //   warps 4-7/8-11  softmax of slot 0 / slot 1, one thread per query row, the whole 128-key row
 //                   of S in registers
 // TMEM (512 columns): per slot 128 columns of O and 128 columns of S.  P (bf16) is written back
@@ -70,8 +71,10 @@ struct Control {
     uint32_t tmem_base;
     int abort;
     Step step[kNM];
-    int colring[256];
+    int colring[512];               // gathered columns waiting for a step: (row-block bits << 28) | position
+    int4 gmsg[2];                   // planner -> V-gather warp, alternating: (step, first ring entry, count, 0); count 0 = done
 };
+static_assert(kCtlOff + sizeof(Control) <= 232448, "shared memory of one CTA");
 
 struct AttnArgs {
     __nv_bfloat16* o;
@@ -139,6 +142,10 @@ struct RangeCursor {
     }
     __device__ __forceinline__ bool live() const { return ri < n && a <= last_row && a < kv_hi; }
 };
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ unsigned long long below64(int x) {   // bits [0, x) for any integer x
     return x >= 64 ? ~0ull : (x <= 0 ? 0ull : ((1ull << x) - 1ull));
@@ -234,6 +241,28 @@ __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned
     mbar_arrive(bar_half1);
 }
 
+// One warp copies `width` gathered rows (256 B each) of K or V into a 128-byte-swizzled stage: lanes 0-15 fetch the
+// sixteen 16-byte pieces of one row, lanes 16-31 those of the next; col[q] holds this lane's row index for rows
+// 32q + lane.  The copies are asynchronous; the caller arrives on the stage barrier with cp_async_arrive_noinc.
+__device__ __forceinline__ void gather_rows(uint32_t dst, const __nv_bfloat16* base, long long row_stride,
+                                            const int (&col)[4], int width, int lane) {
+    const int chunk = lane & 15, sub = lane >> 4;
+    const uint32_t half_off = (uint32_t)(chunk >> 3) * 16384u;                  // which 64-column half of the stage
+    const char* src0 = reinterpret_cast<const char*>(base + chunk * 8);
+    const long long stride_b = row_stride * 2;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (32 * q >= width) break;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+            const int rr = 2 * i + sub;
+            const int c = __shfl_sync(0xffffffffu, col[q], rr);
+            const int r = 32 * q + rr;
+            cp_async_16(dst + half_off + (uint32_t)r * 128u + (uint32_t)(((chunk ^ r) & 7) << 4), src0 + (long long)c * stride_b);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(384, 1)
 sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -308,6 +337,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             }
         }
         int step = 0;
+        int n_gather = 0;              // gather steps handed to the V-gather warp so far
         unsigned issued = 0;           // 64x64 tile equivalents this CTA sends to the tensor pipe
         bool ok = true;
         bool bad_plan = false;         // the plan of this head cannot have been written by the plan builders
@@ -487,7 +517,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     val[q4] = lane + 32 * q4 < count;
-                    e[q4] = ctl->colring[(emitted + 32 * q4 + lane) & 255];
+                    e[q4] = ctl->colring[(emitted + 32 * q4 + lane) & 511];
                 }
                 unsigned long long mk[4][2];
 #pragma unroll
@@ -498,6 +528,11 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     mk[r][0] = (unsigned long long)bl[0] | ((unsigned long long)bl[1] << 32);
                     mk[r][1] = (unsigned long long)bl[2] | ((unsigned long long)bl[3] << 32);
                 }
+                // hand the step to the V-gather warp (warp 2) before any wait of this warp can fail: both meet at
+                // named barrier 2 once per gather step and once more when the planner is done
+                if (lane == 0) ctl->gmsg[n_gather & 1] = make_int4(step, emitted, count, 0);
+                ++n_gather;
+                named_bar_sync(2, 64);
                 if (!publish(kGatherStep, 0, width, mk)) return;
                 int col[4];      // local key rows
 #pragma unroll
@@ -505,36 +540,9 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     col[q4] = val[q4] ? (e[q4] & 0x0fffffff) - a.kv_pos0 : 0;
                     if (!MINF_IN_BOUNDS(a.status, col[q4] >= 0 && col[q4] < a.n_kv)) col[q4] = 0;
                 }
-                const int chunk = lane & 15, sub = lane >> 4;
-                const int iters = width / 2;
                 if (!wait_use(ctl->k_empty, kNK, step)) return;
-                {
-                    const uint32_t dst = smem_base + kKOff + (step % kNK) * kTile;
-                    const __nv_bfloat16* kb = a.k + b * a.k_sb + hk * a.k_sh;
-#pragma unroll 4
-                    for (int it = 0; it < iters; ++it) {
-                        const int r = 2 * it + sub;
-                        const int src_lane = r & 31, q4 = r >> 5;
-                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
-                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
-                        cp_async_16(dst + off, kb + (long long)c * a.k_sn + chunk * 8);
-                    }
-                    cp_async_arrive_noinc(bar(&ctl->k_full[step % kNK]));      // this lane's K rows, whenever they land
-                }
-                if (!wait_use(ctl->v_empty, kNV, step)) return;
-                {
-                    const uint32_t dst = smem_base + kVOff + (step % kNV) * kTile;
-                    const __nv_bfloat16* vb = a.v + b * a.v_sb + hk * a.v_sh;
-#pragma unroll 4
-                    for (int it = 0; it < iters; ++it) {
-                        const int r = 2 * it + sub;
-                        const int src_lane = r & 31, q4 = r >> 5;
-                        const int c = __shfl_sync(0xffffffffu, q4 == 0 ? col[0] : q4 == 1 ? col[1] : q4 == 2 ? col[2] : col[3], src_lane);
-                        const uint32_t off = (uint32_t)(chunk >> 3) * 16384u + (uint32_t)r * 128u + (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
-                        cp_async_16(dst + off, vb + (long long)c * a.v_sn + chunk * 8);
-                    }
-                    cp_async_arrive_noinc(bar(&ctl->v_full[step % kNV]));      // ... and its V rows (the planner does not wait)
-                }
+                gather_rows(smem_base + kKOff + (step % kNK) * kTile, a.k + b * a.k_sb + hk * a.k_sh, a.k_sn, col, width, lane);
+                cp_async_arrive_noinc(bar(&ctl->k_full[step % kNK]));      // each lane's K rows, whenever they land
                 emitted += count;
                 ++step;
             };
@@ -558,7 +566,7 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                     int e = colv & 0x0fffffff;
 #pragma unroll
                     for (int r = 0; r < 4; ++r) e |= (int)((wr[r] >> lane) & 1u) << (28 + r);
-                    ctl->colring[pos & 255] = e;
+                    ctl->colring[pos & 511] = e;
                 }
                 filled += __popc(sel);
                 __syncwarp();
@@ -566,6 +574,8 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
             }
             if (ok && filled > emitted) flush_chunk(filled - emitted);
         }
+        if (lane == 0) ctl->gmsg[n_gather & 1] = make_int4(0, 0, 0, 0);      // no more gather steps
+        named_bar_sync(2, 64);
         if (ok) {
             // the end marker travels like a step: the MMA warp reads a step's descriptor once the
             // step's K stage is full, so the marker completes a K stage too (with no load)
@@ -690,7 +700,31 @@ sparse_attn_fwd_kernel(const __grid_constant__ Maps tm, const AttnArgs a) {
                 umma_commit(bar(&ctl->o_done[1]));
             }
         }
-    } else if (warp < 4) {
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ V rows of the gather steps
+        // The planner copies the K rows of a gather step, this warp its V rows: issuing the 16-byte copies is what
+        // a gather step costs, and two warps halve it.  The warps meet at named barrier 2 per step.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        bool ok = true;
+        for (int g = 0;; ++g) {
+            named_bar_sync(2, 64);
+            const int4 msg = ctl->gmsg[g & 1];          // (step, first ring entry, count)
+            if (msg.z == 0) break;
+            if (!ok) continue;                          // keep meeting the planner until it is done
+            const int step = msg.x, width = msg.z > 64 ? 128 : 64;
+            int col[4];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int e = ctl->colring[(msg.y + 32 * q4 + lane) & 511];
+                col[q4] = lane + 32 * q4 < msg.z ? (e & 0x0fffffff) - a.kv_pos0 : 0;
+                if (!MINF_IN_BOUNDS(a.status, col[q4] >= 0 && col[q4] < a.n_kv)) col[q4] = 0;
+            }
+            const int s = step % kNV, use = step / kNV;
+            if (use > 0 && !mbar_wait(bar(&ctl->v_empty[s]), (use - 1) & 1, abort_flag)) { ok = false; continue; }
+            gather_rows(smem_base + kVOff + s * kTile, a.v + b * a.v_sb + hk * a.v_sh, a.v_sn, col, width, lane);
+            cp_async_arrive_noinc(bar(&ctl->v_full[s]));
+        }
+    } else if (warp == 3) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
