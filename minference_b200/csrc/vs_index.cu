@@ -237,17 +237,19 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
                 const bool valid = base + lane < n_cand;
                 const int j = valid ? cand[base + lane] : 1;
                 const int e = max(end_m - s_list[j], 64), prev = max(end_m - s_list[j - 1], 64);
-                unsigned open = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
-                while (open) {
-                    const int l = __ffs(open) - 1;
-                    open &= open - 1;
-                    const int ej = __shfl_sync(0xffffffffu, e, l);
+                // Under a given range start every lane can test its own entry; the first lane whose entry opens a
+                // new range is the next start, and only the lanes after it are tested again: one ballot per range
+                // instead of one shuffle pair per candidate.
+                unsigned todo = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
+                while (todo) {
+                    const int re_mine = e_first + ((prev - e_first + 63) & ~63);
+                    const unsigned opens = __ballot_sync(0xffffffffu, ((todo >> lane) & 1u) && e > re_mine + 64);
+                    if (opens == 0u) break;
+                    const int l = __ffs(opens) - 1;
                     const int pj = __shfl_sync(0xffffffffu, prev, l);
-                    const int re = e_first + ((pj - e_first + 63) & ~63);
-                    if (ej > re + 64) {
-                        close_range(e_first - 64, re);
-                        e_first = ej;
-                    }
+                    close_range(e_first - 64, e_first + ((pj - e_first + 63) & ~63));
+                    e_first = __shfl_sync(0xffffffffu, e, l);
+                    todo &= ~((2u << l) - 1u);          // entries up to and including l are settled
                 }
             }
             const int e_last = max(end_m - s_list[nnz_s - 1], 64);
