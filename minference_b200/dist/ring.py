@@ -154,6 +154,37 @@ def slash_window(n_ctx: int, chunk: int, c: int):
     return lo, hi
 
 
+def rank_score_pack(score_pass, chunks, n_ctx: int, c: int, B: int, H: int, dev) -> torch.Tensor:
+    """What one rank contributes to the score exchange, ``[B, H, 2, c + (c + 64)]``: per owned chunk the vertical
+    scores of its ``c`` keys and the window of diagonal offsets those keys reach (``slash_window``).
+    ``score_pass(i, vertical, slash)`` runs the score pass of the rank's i-th chunk into full-length arrays.  The two
+    chunks are scored one after the other, each into a cleared window: the middle rank's chunks are neighbours, and
+    the 63 offsets their windows share must not be summed before the exchange."""
+    scores = torch.empty((2, B, H, n_ctx), dtype=torch.float32, device=dev)
+    pack = torch.zeros((B, H, 2, 2 * c + 64), dtype=torch.float32, device=dev)
+    for i, ci in enumerate(chunks):
+        lo, hi = slash_window(n_ctx, ci, c)
+        scores[1][:, :, lo:hi].zero_()
+        score_pass(i, scores[0], scores[1])
+        pack[:, :, i, :c] = scores[0][:, :, ci * c:(ci + 1) * c]
+        pack[:, :, i, c:c + hi - lo] = scores[1][:, :, lo:hi]
+    return pack
+
+
+def assemble_scores(everyone: torch.Tensor, n_ctx: int, c: int, world: int) -> torch.Tensor:
+    """``[world, B, H, 2, 2c + 64]`` (every rank's pack) -> ``[2, B, H, n_ctx]`` vertical and slash scores of the whole
+    sequence.  Chunks are added in ascending order, so the 63 offsets two neighbouring chunks share are summed in
+    a fixed order (and a sum of two terms does not depend on it anyway)."""
+    B, H = everyone.shape[1], everyone.shape[2]
+    scores = torch.zeros((2, B, H, n_ctx), dtype=torch.float32, device=everyone.device)
+    for chunk in range(2 * world):
+        r, i = (chunk, 0) if chunk < world else (2 * world - 1 - chunk, 1)
+        lo, hi = slash_window(n_ctx, chunk, c)
+        scores[0][:, :, chunk * c:(chunk + 1) * c] = everyone[r, :, :, i, :c]
+        scores[1][:, :, lo:hi] += everyone[r, :, :, i, c:c + hi - lo]
+    return scores
+
+
 def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_size, group=None,
                                  cap_v: int | None = None, cap_s: int | None = None):
     """Global index lists from sharded K: ``(v_idx, s_idx, nnz_v, nnz_s)``, identical on all ranks.
@@ -180,15 +211,16 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_
     chunks = owned_chunks(rank, world)
     k_parts = [k_loc[:, :, :c], k_loc[:, :, c:]]
 
-    def run(pass_, stats_t, total, row_stats, vertical, slash):
-        for i, (ci, kp) in enumerate(zip(chunks, k_parts)):
-            with torch.cuda.device(dev):
-                _cabi.check(L.minf_vs_scores_pass(
-                    pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
-                    B, H, Hkv, n_ctx, c, ci * c, D, _cabi.ptr(stats_t), i * bl, total, _cabi.ptr(row_stats),
-                    _cabi.ptr(vertical), _cabi.ptr(slash), _cabi.ptr(status), _cabi.stream_ptr(dev)))
+    def run(pass_, i, stats_t, total, row_stats, vertical, slash):
+        ci, kp = chunks[i], k_parts[i]
+        with torch.cuda.device(dev):
+            _cabi.check(L.minf_vs_scores_pass(
+                pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
+                B, H, Hkv, n_ctx, c, ci * c, D, _cabi.ptr(stats_t), i * bl, total, _cabi.ptr(row_stats),
+                _cabi.ptr(vertical), _cabi.ptr(slash), _cabi.ptr(status), _cabi.stream_ptr(dev)))
 
-    run(1, stats, 2 * bl, None, None, None)
+    for i in range(2):
+        run(1, i, stats, 2 * bl, None, None, None)
     gathered = torch.empty((world,) + tuple(stats.shape), dtype=torch.float32, device=dev)
     dist.all_gather_into_tensor(gathered, stats, group=group)
     all_stats = _ordered_blocks(gathered, world, bl)            # [B*H, 64, 2*world*bl, 2], ascending key order
@@ -196,23 +228,11 @@ def ring_vertical_slash_estimate(q_loc, k_loc, n_ctx: int, vertical_size, slash_
     with torch.cuda.device(dev):
         _cabi.check(L.minf_vs_scores_combine(_cabi.ptr(all_stats), B, H, all_stats.shape[2], _cabi.ptr(row_stats),
                                              _cabi.stream_ptr(dev)))
-    scores = torch.zeros((2, B, H, n_ctx), dtype=torch.float32, device=dev)
-    run(2, None, 2 * world * bl, row_stats, scores[0], scores[1])
-    # every rank contributes the vertical scores of its own keys and the diagonal offsets those keys reach
-    wins = [slash_window(n_ctx, ci, c) for ci in chunks]
-    width = c + 64
-    pack = torch.zeros((B, H, 2, c + width), dtype=torch.float32, device=dev)
-    for i, (ci, (lo, hi)) in enumerate(zip(chunks, wins)):
-        pack[:, :, i, :c] = scores[0][:, :, ci * c:(ci + 1) * c]
-        pack[:, :, i, c:c + hi - lo] = scores[1][:, :, lo:hi]
+    pack = rank_score_pack(lambda i, vertical, slash: run(2, i, None, 2 * world * bl, row_stats, vertical, slash),
+                           chunks, n_ctx, c, B, H, dev)
     everyone = torch.empty((world,) + tuple(pack.shape), dtype=torch.float32, device=dev)
     dist.all_gather_into_tensor(everyone, pack, group=group)
-    scores[1].zero_()
-    for chunk in range(2 * world):          # ascending chunk order: the 63 shared offsets are added in a fixed order
-        r, i = (chunk, 0) if chunk < world else (2 * world - 1 - chunk, 1)
-        lo, hi = slash_window(n_ctx, chunk, c)
-        scores[0][:, :, chunk * c:(chunk + 1) * c] = everyone[r, :, :, i, :c]
-        scores[1][:, :, lo:hi] += everyone[r, :, :, i, c:c + hi - lo]
+    scores = assemble_scores(everyone, n_ctx, c, world)
     if torch.is_tensor(vertical_size):
         vs = vertical_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()
         ss = slash_size.to(device=dev, dtype=torch.int32).repeat(B).contiguous()

@@ -155,6 +155,54 @@ def test_sharded_estimator_stages_match_whole_sequence(dev, n, world):
             break
 
 
+@pytest.mark.parametrize("n,world", [(8192, 2), (32768, 4), (65536, 8)])
+def test_score_exchange_of_emulated_ranks_reproduces_whole_sequence_scores(dev, n, world):
+    """The pack every rank sends (its keys' vertical scores + the diagonal offsets they reach) and the assembly of all
+    packs, with the ranks emulated one after the other: bit-identical to the whole-sequence estimator, including the
+    middle rank whose two chunks are neighbours."""
+    from minference_b200 import _cabi
+    from minference_b200.dist import ring
+    from minference_b200.modules.minference_forward import vertical_slash_estimate
+    from minference_b200.synthetic import make_qkv
+
+    hq, hkv = 4, 2
+    q, k, _ = make_qkv(n, hq, hkv, seed=13, dtype=torch.bfloat16)
+    dq, dk = q.to(dev), k.to(dev)
+    *_, vs_ref, ss_ref = vertical_slash_estimate(dq, dk, 200, 600, return_scores=True)
+    L = _cabi.lib()
+    c = ring.chunk_size(n, world)
+    assert c % 2048 == 0
+    bl = L.minf_vs_scores_blocks(c)
+    q_last = dq[:, :, -64:].contiguous()
+    status = _cabi.new_status(dev)
+
+    def score_pass(pass_, kp, ci, stats, offset, total, row_stats, vertical, slash):
+        _cabi.check(L.minf_vs_scores_pass(pass_, _cabi.ptr(q_last), _cabi.ptr(kp), _cabi.strides3(q_last), _cabi.strides3(kp),
+                                          1, hq, hkv, n, c, ci * c, 128, _cabi.ptr(stats), offset, total, _cabi.ptr(row_stats),
+                                          _cabi.ptr(vertical), _cabi.ptr(slash), _cabi.ptr(status), _cabi.stream_ptr(dev)))
+
+    per_rank = []
+    for r in range(world):
+        stats = torch.empty((hq, 64, 2 * bl, 2), dtype=torch.float32, device=dev)
+        for i, ci in enumerate(ring.owned_chunks(r, world)):
+            score_pass(1, dk[:, :, ci * c:(ci + 1) * c], ci, stats, i * bl, 2 * bl, None, None, None)
+        per_rank.append(stats)
+    all_stats = ring._ordered_blocks(torch.stack(per_rank), world, bl)
+    row_stats = torch.empty((hq, 64, 2), dtype=torch.float32, device=dev)
+    _cabi.check(L.minf_vs_scores_combine(_cabi.ptr(all_stats), 1, hq, all_stats.shape[2], _cabi.ptr(row_stats), _cabi.stream_ptr(dev)))
+    packs = []
+    for r in range(world):
+        chunks = ring.owned_chunks(r, world)
+        packs.append(ring.rank_score_pack(
+            lambda i, vertical, slash: score_pass(2, dk[:, :, chunks[i] * c:(chunks[i] + 1) * c], chunks[i], None, 0,
+                                                  2 * world * bl, row_stats, vertical, slash),
+            chunks, n, c, 1, hq, dev))
+    scores = ring.assemble_scores(torch.stack(packs), n, c, world)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert torch.equal(scores[0], vs_ref) and torch.equal(scores[1], ss_ref)
+
+
 @pytest.mark.parametrize("world,n,n_init,n_local", [(2, 4096, 128, 512), (4, 8192, 64, 1500)])
 def test_windowed_kernel_pairs_merge_mixed_a_shape_and_vertical_slash(dev, world, n, n_init, n_local):
     """Heads 0 and 2 vertical-slash, heads 1 and 3 A-shape, in the same windowed launches."""
