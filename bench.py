@@ -254,9 +254,13 @@ def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=No
     from minference_b200.ops.block_sparse_flash_attention import build_block_sparse_plan
     from minference_b200.ops.pit_sparse_flash_attention_v2 import build_vertical_slash_plan
     from minference_b200.ops.sparse_forward import SparsePlan, sparse_attention_forward
-    from minference_b200.synthetic import local_vs_indices, make_qkv, scattered_vs_indices
+    from minference_b200.synthetic import local_vs_indices, make_qkv, make_qkv_ranges, scattered_vs_indices
 
-    if q is None:
+    if q is None and seed == 0 and any(spec[0] == n for spec in RING_WORKLOADS.values()):
+        # the sequence the ring workloads shard (the generator keyed by fixed blocks): the one-GPU anchor of those
+        # lines computes on the same values, so tiles_per_layer can be compared across GPU counts
+        q, k, v = make_qkv_ranges(n, [(0, n)], hq, hkv, seed=0, dtype=torch.bfloat16, device=dev)
+    elif q is None:
         q, k, v = make_qkv(n, hq, hkv, seed=seed, dtype=torch.bfloat16, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
     events = {"est": [], "plan": [], "attn": []}

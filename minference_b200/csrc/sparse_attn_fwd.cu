@@ -167,7 +167,10 @@ __device__ __forceinline__ void upto128(int lim, unsigned long long& w0, unsigne
 // (Skipping the exponentials of a 32- or 64-key part that no row of the warp can see -- the other row
 // block's half of an isolated diagonal -- was built and measured in two forms: it changed nothing on
 // scattered index sets, whose steps are bound by the softmax -> PV -> QK^T chain of a slot and not by the
-// MUFU, and it cost 4 % on dense ones, so every chunk is processed.)
+// MUFU, and it cost 4 % on dense ones, so every chunk is processed.  Taking a quarter or half of the
+// exponentials from a cubic on the FMA pipe (packed two-wide arithmetic, exponent written by an integer add)
+// was measured as well: 1 % and 9 % slower on dense index sets, 9 % and 17 % on scattered ones -- the cubic's
+// ten instructions per key pair cost a softmax warp more time than the two MUFU operations they replace.)
 template <int NCH>
 __device__ __forceinline__ void softmax_row(uint32_t t_s, uint32_t t_o, unsigned long long m0, unsigned long long m1,
                                             float scale_log2, bool have_o, float& m_ref, float& l_sum,

@@ -69,34 +69,44 @@ def make_qkv(n: int, hq: int, hkv: int, d: int = 128, seed: int = 0, dtype=torch
     return q, k, v
 
 
+STREAM_BLOCK = 1 << 16
+
+
 def make_qkv_ranges(n: int, ranges, hq: int, hkv: int, d: int = 128, seed: int = 0, dtype=torch.bfloat16,
                     device="cpu", theta: float = 5e5, plant: bool = True):
-    """Like ``make_qkv`` for a sequence of ``n`` tokens, but only the token ranges
-    ``[(start, length), ...]`` are generated (concatenated in that order): the shard a rank owns
-    under sequence parallelism.  Positions, and therefore the rotary phases and the planted
-    columns, are those of the whole sequence; the random stream is keyed by (seed, start)."""
+    """Token ranges ``[(start, length), ...]`` (concatenated in that order) of one fixed sequence of ``n`` tokens:
+    the shard a rank owns under sequence parallelism, or with ``[(0, n)]`` the whole sequence.  Positions, and
+    therefore the rotary phases and the planted columns, are those of the whole sequence, and the random stream is
+    keyed by (seed, 65536-token block), so every split of the sequence sees the same values.  (``make_qkv`` draws one
+    stream from token 0 on and gives a different sequence.)"""
     dev = torch.device(device)
     gu = torch.Generator().manual_seed(seed + 104729)
     u = torch.nn.functional.normalize(torch.randn(d, generator=gu), dim=0).to(dev)
     planted = planted_positions(n, seed).to(dev) if plant else None
     qs, ks, vs = [], [], []
     for start, length in ranges:
-        g = torch.Generator(device=dev).manual_seed(seed * 1000003 + start)
         q = torch.empty(1, hq, length, d, dtype=dtype, device=dev)
         k = torch.empty(1, hkv, length, d, dtype=dtype, device=dev)
         v = torch.empty(1, hkv, length, d, dtype=dtype, device=dev)
-        for s0 in range(0, length, 1 << 16):
-            e0 = min(s0 + (1 << 16), length)
-            cos, sin = rope_cos_sin(e0 - s0, d, theta, dev, start=start + s0)
-            qc = apply_rope(torch.randn(1, hq, e0 - s0, d, generator=g, device=dev), cos, sin)
-            kc = apply_rope(torch.randn(1, hkv, e0 - s0, d, generator=g, device=dev), cos, sin)
-            vc = torch.randn(1, hkv, e0 - s0, d, generator=g, device=dev)
+        for blk in range(start // STREAM_BLOCK, (start + length - 1) // STREAM_BLOCK + 1):
+            b0 = blk * STREAM_BLOCK
+            bl = min(STREAM_BLOCK, n - b0)
+            g = torch.Generator(device=dev).manual_seed(seed * 1000003 + blk)
+            cos, sin = rope_cos_sin(bl, d, theta, dev, start=b0)
+            qc = apply_rope(torch.randn(1, hq, bl, d, generator=g, device=dev), cos, sin)
+            kc = apply_rope(torch.randn(1, hkv, bl, d, generator=g, device=dev), cos, sin)
+            vc = torch.randn(1, hkv, bl, d, generator=g, device=dev)
             if plant:
                 qc = qc + u
-                sel = planted[(planted >= start + s0) & (planted < start + e0)] - (start + s0)
+                sel = planted[(planted >= b0) & (planted < b0 + bl)] - b0
                 kc[:, :, sel] += 3.0 * u
-            q[:, :, s0:e0] = qc.to(dtype); k[:, :, s0:e0] = kc.to(dtype); v[:, :, s0:e0] = vc.to(dtype)
+            lo, hi = max(start, b0), min(start + length, b0 + bl)          # the part of the block inside the range
+            q[:, :, lo - start:hi - start] = qc[:, :, lo - b0:hi - b0].to(dtype)
+            k[:, :, lo - start:hi - start] = kc[:, :, lo - b0:hi - b0].to(dtype)
+            v[:, :, lo - start:hi - start] = vc[:, :, lo - b0:hi - b0].to(dtype)
         qs.append(q); ks.append(k); vs.append(v)
+    if len(qs) == 1:
+        return qs[0], ks[0], vs[0]
     return torch.cat(qs, dim=2), torch.cat(ks, dim=2), torch.cat(vs, dim=2)
 
 
