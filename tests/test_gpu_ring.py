@@ -279,5 +279,6 @@ def test_real_ring_on_two_gpus():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29517", os.path.join(ROOT, "tests", "multi_gpu_ring_check.py")]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(p.stdout[-2000:])
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert "RING_OK" in p.stdout
