@@ -163,6 +163,19 @@ int minf_vs_estimate(
     void* scratch, int32_t* status, void* stream);
 
 /*
+ * Attention plan from a block mask (the index set of the reference's FlexPrefill path: flattened block ids built at
+ * modules/flexprefill.py:903-927 and walked per query block by its kernel at :353-495).  `mask` is
+ * [batch*heads, nb, nb] bytes, nb = ceil(context_size / block_tokens), entry (i, j) non-zero <=> query block i
+ * attends key block j; entries with j > i are ignored and every block is causal inside.  block_tokens is a multiple
+ * of 64.  Runs of neighbouring key blocks become one token range of the plan; `cap_s` is the largest number of runs a
+ * row of the mask may have (more sets bit 2 of status[MINF_ST_ERROR]).  The plan holds minf_plan_bytes(batch, heads,
+ * context_size, 0, cap_s) bytes and is consumed by minf_sparse_attention_fwd with cap_v = 0.
+ */
+int minf_block_mask_build_plan(
+    const uint8_t* mask, int batch, int heads, int context_size, int block_tokens, int cap_s,
+    void* plan, int32_t* status, void* stream);
+
+/*
  * The stages of minf_vs_estimate as separate calls, for callers that hold only part of the keys
  * (sequence sharding): statistics pass over the local keys, exchange of the per-block statistics,
  * combination, score pass, reduction of the score arrays over the ranks, selection.
@@ -190,6 +203,19 @@ int minf_vs_scores_pass(
     float* vertical_scores, float* slash_scores,
     int32_t* status, void* stream);
 int minf_vs_scores_combine(const void* stats, int batch, int hq, int blocks_total, void* row_stats, void* stream);
+/*
+ * minf_vs_scores_pass with the divisor of the logits given by the caller instead of sqrt(head_dim): the bf16 product
+ * q_last . k is divided by `logit_divisor` and rounded to bf16 again.  With 1.0 the product is used as it is, which
+ * is what the FlexPrefill estimator needs: it scales the queries first and rounds once
+ * (modules/flexprefill.py:968-975 of the reference).
+ */
+int minf_vs_scores_pass_divisor(
+    int pass, const void* q_last, const void* k,
+    const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim, float logit_divisor,
+    void* stats, int block_offset, int blocks_total, const void* row_stats,
+    float* vertical_scores, float* slash_scores,
+    int32_t* status, void* stream);
 /*
  * Per-head top-k over the score arrays.  The first `force_columns` keys and the `force_diagonals` nearest
  * diagonals are always taken and budgets are raised to `min_vertical` / `min_slash`: 30, 100, 30, 50 for the

@@ -48,6 +48,9 @@ SIGNATURES = {
     "minf_vs_scores_blocks": (c_int, [c_int]),
     "minf_vs_scores_pass": (c_int, [c_int, c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 7 +
                             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "minf_vs_scores_pass_divisor": (c_int, [c_int, c_void_p, c_void_p, _I64x3, _I64x3] + [c_int] * 7 + [c_float] +
+                                    [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "minf_block_mask_build_plan": (c_int, [c_void_p] + [c_int] * 5 + [c_void_p, c_void_p, c_void_p]),
     "minf_vs_scores_combine": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "minf_vs_select_scratch_bytes": (c_size_t, [c_int] * 3),
     "minf_vs_select": (c_int, [c_void_p, c_void_p] + [c_int] * 3 + [c_void_p, c_void_p, c_int, c_int] +

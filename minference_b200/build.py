@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libminfer_b200.so")
-SOURCES = ["cabi.cu", "vs_index.cu", "sparse_attn_fwd.cu", "vs_estimate.cu", "block_sparse_index.cu"]
+SOURCES = ["cabi.cu", "vs_index.cu", "sparse_attn_fwd.cu", "vs_estimate.cu", "block_sparse_index.cu", "block_mask_plan.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",

@@ -635,6 +635,17 @@ extern "C" int minf_vs_scores_pass(
     int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim,
     void* stats, int block_offset, int blocks_total, const void* row_stats,
     float* vertical_scores, float* slash_scores, int32_t* status, void* stream) {
+    return minf_vs_scores_pass_divisor(pass, q_last, k, q_strides, k_strides, batch, hq, hkv, context_size, n_k, col_base,
+                                       head_dim, sqrtf((float)head_dim), stats, block_offset, blocks_total, row_stats,
+                                       vertical_scores, slash_scores, status, stream);
+}
+
+extern "C" int minf_vs_scores_pass_divisor(
+    int pass, const void* q_last, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+    int batch, int hq, int hkv, int context_size, int n_k, int col_base, int head_dim, float logit_divisor,
+    void* stats, int block_offset, int blocks_total, const void* row_stats,
+    float* vertical_scores, float* slash_scores, int32_t* status, void* stream) {
+    if (!(logit_divisor > 0.f)) return fail(MINF_E_ARG, "logit_divisor must be positive");
     if (!q_last || !k || !status) return fail(MINF_E_ARG, "null pointer argument");
     if (pass != 1 && pass != 2) return fail(MINF_E_ARG, "pass must be 1 or 2");
     if (pass == 1 && !stats) return fail(MINF_E_ARG, "pass 1 needs the statistics array");
@@ -659,7 +670,7 @@ extern "C" int minf_vs_scores_pass(
     a.stats = static_cast<float2*>(stats);
     a.row_stats = static_cast<const float2*>(row_stats);
     a.vertical = vertical_scores; a.slash = slash_scores;
-    a.sqrt_d = sqrtf((float)head_dim);
+    a.sqrt_d = logit_divisor;
     a.rcp_sqrt_d = 1.0f / a.sqrt_d;
     a.status = status;
     CUtensorMap tq, tk;

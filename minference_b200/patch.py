@@ -17,6 +17,7 @@ import torch
 
 import warnings
 
+from .modules.flexprefill import flexprefill_forward
 from .modules.minference_forward import minference_prefill_forward, static_prefill_forward
 from .modules.tri_mix import tri_mix_forward, tri_mix_minference_forward
 from .ops.pit_sparse_flash_attention_v2 import dilated_sparse_attention
@@ -32,6 +33,7 @@ prefill_forwards = {
     "tri_mix": tri_mix_forward,
     "tri_mix_minference": tri_mix_minference_forward,
     "static": static_prefill_forward,
+    "flexprefill": flexprefill_forward,
     "dilated1": lambda q, k, v, kw: dilated_sparse_attention(q, k, v, "dilated1"),
     "dilated2": lambda q, k, v, kw: dilated_sparse_attention(q, k, v, "dilated2"),
 }

@@ -331,3 +331,153 @@ def streaming_attention_oracle(q, k, v, n_init, n_local, row_blocks=None):
                 out[b, h, i * 64:i * 64 + (r1 - r0)] = masked_attention_rows(
                     q[b, h, r0:r1], k[b, h // rep], v[b, h // rep], mask, r0)
     return out
+
+
+# ---------------------------------------------------------------------------------
+# FlexPrefill  (modules/flexprefill.py:880-1112)
+# ---------------------------------------------------------------------------------
+
+def flex_score_cover_topk(x: torch.Tensor, score: float) -> torch.Tensor:
+    """How many of the largest entries it takes to pass ``score`` in sum (:880-883)."""
+    cumsum_x = torch.cumsum(torch.sort(x, dim=-1, descending=True).values, dim=-1)
+    return torch.sum(cumsum_x <= score, dim=-1) + 1
+
+
+def flex_sum_pool(x: torch.Tensor, kernel: int) -> torch.Tensor:
+    """Sums over consecutive groups of ``kernel`` entries of the last axis, the tail zero-padded (:866-877)."""
+    n = x.shape[-1]
+    x = torch.nn.functional.pad(x, (0, math.ceil(n / kernel) * kernel - n), value=0)
+    return x.view(*x.shape[:-1], -1, kernel).sum(-1)
+
+
+def flex_avg_pool_rows(x: torch.Tensor, kernel: int) -> torch.Tensor:
+    """Mean over consecutive groups of ``kernel`` rows of ``[B,H,N,D]``, a short last group divided by its own
+    length, result in the input dtype (the reference's pooling kernel, :662-727, pool type "avg")."""
+    B, H, N, D = x.shape
+    nb = math.ceil(N / kernel)
+    xp = torch.nn.functional.pad(x.float(), (0, 0, 0, nb * kernel - N))
+    cnt = torch.full((nb,), float(kernel))
+    cnt[-1] = N - (nb - 1) * kernel
+    return (xp.view(B, H, nb, kernel, D).sum(3) / cnt[None, None, :, None]).to(x.dtype)
+
+
+def flex_sum_all_diagonal_matrix(mat: torch.Tensor) -> torch.Tensor:
+    """``[b,h,n,m] -> [b,h,m]``: entry j is ``sum_i mat[i, i + j + 1 - n]`` (:893-900, the zero-pad + strided view
+    written as an index-add)."""
+    b, h, n, m = mat.shape
+    j = torch.arange(m)[None, :] - torch.arange(n)[:, None] + n - 1          # 0 .. n+m-2
+    out = torch.zeros(b, h, n + m - 1, dtype=mat.dtype)
+    out.index_add_(2, j.reshape(-1), mat.reshape(b, h, n * m))
+    return out[..., :m]
+
+
+def flex_square_root_js_divergence(p: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
+    m = (p + q) / 2                                                          # :946-950
+    return torch.sqrt(0.5 * (p * torch.log(p / m)).sum(-1) + 0.5 * (q * torch.log(q / m)).sum(-1))
+
+
+def flex_active_block_mask(q: torch.Tensor, k: torch.Tensor, block_size: int, gamma: float, min_budget: int,
+                           max_budget: int, tau: float = 0.0, return_details: bool = False):
+    """``get_active_blocks`` (:953-1067) for ``[B,H,N,D]`` queries and ``[B,Hkv,N,D]`` keys (query head h reads KV
+    head ``h // (H/Hkv)``, the non-interleaved grouping), budgets in blocks.  Returns the block set as a boolean
+    matrix ``[B,H,nb,nb]`` (entry (i, j): query block i attends key block j) instead of the reference's lists of
+    flattened ids ``i*nb + j``; block (0, 0), which the reference's padding value 0 stands for, is always in the set
+    because the first key block and the main block diagonal are forced.
+    """
+    B, H, N, D = q.shape
+    Hkv = k.shape[1]
+    rep = H // Hkv
+    nb = math.ceil(N / block_size)
+    max_budget = min(max_budget, nb)
+    kk = k.repeat_interleave(rep, dim=1) if rep > 1 else k
+    last_q = q[:, :, -block_size:, :] / math.sqrt(D)                         # :968 (rounds in the input dtype)
+    qk = torch.einsum("bhid,bhjd->bhij", last_q, kk)                         # :969-980, product in the input dtype
+    bs = last_q.shape[2]
+    causal = torch.arange(bs)[:, None] >= torch.arange(bs)[None, :]
+    qk[..., -bs:].masked_fill_(~causal, float("-inf"))                       # :981-988
+    qk = torch.softmax(qk, dim=-1, dtype=torch.float32)                      # :990
+    slash = flex_sum_all_diagonal_matrix(qk) / qk.shape[-2]                  # :992, index j <-> offset N-1-j
+    vertical = qk.mean(-2)                                                   # :993
+    n_vert = flex_score_cover_topk(vertical, gamma) // 128 + 1               # :995-996 (128 is a constant there)
+    n_slash = flex_score_cover_topk(slash, gamma) // 128 + 1
+    n_vert = n_vert.clamp(min_budget, max_budget)                            # :997-1000
+    n_slash = n_slash.clamp(min_budget, max_budget)
+    vertical = flex_sum_pool(vertical, block_size)                           # :1002-1003
+    slash = flex_sum_pool(slash, block_size)
+    avg_k = flex_avg_pool_rows(kk, block_size)                               # :1005-1008
+    avg_qk = torch.einsum("bhd,bhjd->bhj", last_q.mean(2), avg_k)           # :1009-1011
+    avg_qk = torch.softmax(avg_qk, dim=-1, dtype=torch.float32)
+    js = flex_square_root_js_divergence(avg_qk, vertical)                    # :1013
+    block_sparse = js < tau                                                  # :1014
+    n_vert = torch.where(block_sparse, torch.full_like(n_vert, min_budget), n_vert)     # :1015-1016
+    n_slash = torch.where(block_sparse, torch.full_like(n_slash, min_budget), n_slash)
+    vertical = vertical.clone()
+    slash = slash.clone()
+    vertical[..., :1] = torch.inf                                            # :1018-1019
+    slash[..., -1:] = torch.inf
+    mask = torch.zeros(B, H, nb, nb, dtype=torch.bool)
+    ii = torch.arange(nb)
+    for b in range(B):
+        for h in range(H):
+            # slash: the n_slash best pooled entries -> block diagonals d = nb-1-index (:1021-1031, :914-917)
+            ks = min(int(n_slash[b, h]), nb)
+            d_sel = (nb - 1) - slash[b, h].topk(ks).indices
+            for d in d_sel.tolist():
+                rows = ii[ii + d < nb] + d
+                mask[b, h, rows, rows - d] = True
+            # vertical: the n_vert best key blocks, for the query blocks at or below them (:1033-1046, :908-913)
+            kv = min(int(n_vert[b, h]), nb)
+            for j in vertical[b, h].topk(kv).indices.tolist():
+                mask[b, h, j:, j] = True
+            if bool(block_sparse[b, h]):                                     # :1049-1066
+                pad_q = nb * block_size - N
+                avg_q = torch.nn.functional.pad(q[b, h], (0, 0, 0, pad_q)).view(nb, block_size, D).mean(1)
+                avg_q[-1] = avg_q[-1] * block_size / (block_size - pad_q)
+                attn = torch.einsum("id,jd->ij", avg_q / math.sqrt(D), avg_k[b, h])
+                attn = attn.masked_fill(~torch.tril(torch.ones(nb, nb, dtype=torch.bool)), float("-inf"))
+                attn = torch.softmax(attn, dim=-1, dtype=torch.float32).view(-1)
+                vals, idx = torch.sort(attn, descending=True)
+                keep = idx[torch.cumsum(vals, dim=-1) <= gamma * nb]         # :886-890
+                mask[b, h].view(-1)[keep] = True
+    if return_details:
+        return mask, {"n_vertical": n_vert, "n_slash": n_slash, "block_sparse": block_sparse, "js": js,
+                      "vertical_pooled": vertical, "slash_pooled": slash}
+    return mask
+
+
+def flex_block_mask_rows(block_mask, n_ctx: int, block_size: int, r0: int, r1: int):
+    """Token-level mask of rows ``r0..r1`` from a ``[nb, nb]`` block set: the selected key blocks of the row's query
+    block, causal inside (:434-436)."""
+    i = np.arange(r0, r1)
+    j = np.arange(n_ctx)
+    sel = np.asarray(block_mask)[(i // block_size)[:, None], (j // block_size)[None, :]]
+    return sel & (j[None, :] <= i[:, None])
+
+
+def flexprefill_attention_oracle(q, k, v, gamma: float, tau: float = 0.0, min_budget=None, max_budget=None,
+                                 block_size: int = 128, row_blocks=None, block_mask=None):
+    """``flex_prefill_attention`` (:1070-1112) as masked-dense fp32 over the block set, ``[B,H,N,D]`` layout.
+    Returns ``(out [B,H,len(row_blocks)*64,D], block_mask)``; sequences too short for the sparse path
+    (:1087-1088) are dense causal."""
+    B, H, N, D = q.shape
+    rep = H // k.shape[1]
+    min_budget = 1 if min_budget is None else min_budget
+    max_budget = 2147483647 if max_budget is None else max_budget
+    nb = math.ceil(N / block_size)
+    if block_mask is None:
+        if N <= max(2 * block_size, math.ceil(min_budget / block_size) * block_size):
+            block_mask = torch.tril(torch.ones(nb, nb, dtype=torch.bool)).expand(B, H, nb, nb)
+        else:
+            block_mask = flex_active_block_mask(q, k, block_size, gamma, math.ceil(min_budget / block_size),
+                                                math.ceil(max_budget / block_size), tau)
+    rows = (N + 63) // 64
+    rbs = list(range(rows)) if row_blocks is None else list(row_blocks)
+    out = torch.zeros(B, H, len(rbs) * 64, D)
+    for b in range(B):
+        for h in range(H):
+            bm = block_mask[b, h].numpy()
+            for i, m in enumerate(rbs):
+                r0, r1 = m * 64, min(m * 64 + 64, N)
+                out[b, h, i * 64:i * 64 + (r1 - r0)] = masked_attention_rows(
+                    q[b, h, r0:r1], k[b, h // rep], v[b, h // rep], flex_block_mask_rows(bm, N, block_size, r0, r1), r0)
+    return out, block_mask

@@ -22,6 +22,8 @@ What is executed is the reference's own code, not this repository's restatement:
   can tell a wrong selection from a near-tie at the top-k boundary.
 * ``block_index_*.npz`` -- ``_build_block_index`` of
   ``minference/ops/block_sparse_flash_attention.py`` loaded by file path.
+* ``flexprefill_*.npz`` -- ``get_active_blocks`` of ``minference/modules/flexprefill.py`` loaded by file
+  path and run on CPU bf16 tensors, with its Triton key-pooling helper replaced by the same mean in torch.
 
 The fixtures are small seeded cases; the tests also compare larger seeded cases through
 sha256 digests stored in ``digests.json``.
@@ -216,6 +218,63 @@ def make_block_fixtures():
                             q=q.numpy(), k=k.numpy(), block_index=bidx.numpy())
 
 
+FLEX_CASES = [  # (seed, n, heads, kv_heads, gamma, tau, min_budget_blocks, max_budget_blocks, planted sinks)
+    (50, 1500, 4, 2, 0.9, 0.1, 1, 1 << 20, True),
+    (51, 2048, 2, 1, 0.95, 0.0, 1, 1 << 20, True),
+    (52, 1100, 2, 2, 0.5, 0.0, 2, 4, True),
+    (53, 3000, 2, 1, 0.9, 0.1, 1, 1 << 20, False),
+    (54, 2500, 2, 1, 0.9, 0.0, 1, 6, False),
+]
+
+
+def flex_case_inputs(seed, n, heads, kv_heads, plant):
+    from minference_b200.synthetic import make_qkv
+
+    return make_qkv(n, heads, kv_heads, seed=seed, dtype=torch.bfloat16, plant=plant)
+
+
+def input_digest(*tensors) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(t.contiguous().view(torch.int16).numpy().tobytes())
+    return h.hexdigest()
+
+
+def make_flexprefill_fixtures():
+    """``flexprefill_*.npz``: ``get_active_blocks`` of ``minference/modules/flexprefill.py`` loaded by file path and
+    executed on CPU bf16 tensors.  Its key pooling is a Triton kernel and cannot run without a GPU, so that one
+    function (``triton_bnhd_pool``, average over blocks of rows, a short last block divided by its own length) is
+    replaced by the same arithmetic in torch; everything else is the reference's code.  The inputs are regenerated
+    from their seed by the test and checked against the stored sha256."""
+    path = os.path.join(REFERENCE, "minference", "modules", "flexprefill.py")
+    spec = importlib.util.spec_from_file_location("ref_flexprefill", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    def pool(x, kernel_size, pool_type="avg"):          # [b, n, h, d]
+        b, n, h, d = x.shape
+        m = math.ceil(n / kernel_size)
+        xp = torch.nn.functional.pad(x.float(), (0, 0, 0, 0, 0, m * kernel_size - n))
+        cnt = torch.full((m,), float(kernel_size))
+        cnt[-1] = n - (m - 1) * kernel_size
+        return (xp.view(b, m, kernel_size, h, d).sum(2) / cnt[None, :, None, None]).to(x.dtype)
+
+    mod.triton_bnhd_pool = pool
+    for (seed, n, heads, kv_heads, gamma, tau, min_b, max_b, plant) in FLEX_CASES:
+        q, k, v = flex_case_inputs(seed, n, heads, kv_heads, plant)
+        mod.causal_mask = None
+        blocks = mod.get_active_blocks(q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous(),
+                                       v.transpose(1, 2).contiguous(), 128, gamma, min_b, max_b, tau)
+        nb = math.ceil(n / 128)
+        mask = np.zeros((heads, nb * nb), dtype=bool)
+        for h in range(heads):
+            mask[h, blocks[0][h].numpy()] = True
+        np.savez_compressed(os.path.join(HERE, f"flexprefill_{seed}.npz"), seed=seed, n=n, heads=heads, kv_heads=kv_heads,
+                            gamma=gamma, tau=tau, min_budget_blocks=min_b, max_budget_blocks=max_b, plant=plant,
+                            block_mask=np.packbits(mask.reshape(heads, nb, nb), axis=-1), nb=nb,
+                            inputs_sha256=input_digest(q, k))
+
+
 def main():
     if not os.path.isdir(REFERENCE):
         sys.exit("no reference tree: set MINFERENCE_REFERENCE to the checked-out tree")
@@ -224,6 +283,7 @@ def main():
     make_estimator_fixtures()
     make_estimator_bf16_fixtures()
     make_block_fixtures()
+    make_flexprefill_fixtures()
     with open(os.path.join(HERE, "digests.json"), "w") as f:
         json.dump(digests, f, indent=1, sort_keys=True)
     print("fixtures written to", HERE)
