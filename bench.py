@@ -65,6 +65,17 @@ MIXED_WORKLOADS = {
 }
 WORKLOADS.update(MIXED_WORKLOADS)
 A_SHAPE = (128, 4096)
+# FlexPrefill layers (adaptive block budgets from the last 128 queries): the reference's defaults, and a variant with
+# the Jensen-Shannon fallback off and the budgets capped at 8192 tokens, which gives a sparse vertical/slash block set
+FLEX_WORKLOADS = {
+    "llama3_8b_128k_flexprefill": (131072, 32, 8, 0, 0),
+    "llama3_8b_128k_flexprefill_b8k": (131072, 32, 8, 0, 0),
+}
+FLEX_PARAMS = {
+    "llama3_8b_128k_flexprefill": {"gamma": 0.9, "tau": 0.1, "block_size": 128},
+    "llama3_8b_128k_flexprefill_b8k": {"gamma": 0.9, "tau": 0.0, "max_budget": 8192, "block_size": 128},
+}
+WORKLOADS.update(FLEX_WORKLOADS)
 
 
 def mixed_pattern_table(hq: int, vsize: int, ssize: int, seed: int = 3):
@@ -108,6 +119,7 @@ def workload_config(wl: str, world: int) -> dict:
            "last_q": 64, "l2": "inputs_exceed_l2",
            "index_set": "band: slash offsets 0..s-1 + seeded vertical columns, given to the operator" if "_local" in wl
            else "scattered: 100 nearest + uniformly drawn diagonals and columns, given to the operator" if "_scattered" in wl
+           else f"FlexPrefill block set, estimated online from the last 128 queries, {FLEX_PARAMS[wl]}" if wl in FLEX_PARAMS
            else "estimated online from the last 64 queries"}
     if ring:
         cfg["parallelism"] = f"one sequence, zigzag ring over {world} ranks, K/V shards by NCCL send/recv"
@@ -214,6 +226,10 @@ def run_reference_arm(args, wl):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    if wl in FLEX_PARAMS:
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm times the vertical-slash, band and mixed workloads; "
+                          "FlexPrefill workloads carry no CPU baseline"}))
+        return
     torch.set_num_threads(os.cpu_count() or 1)
     vals = []
     desc = ""
@@ -242,13 +258,15 @@ def run_reference_arm(args, wl):
 # kernels of this library per step: estimator (2 score passes, combine, 3 histogram levels, count, write) = 8,
 # plan 1, attention 1; the mixed workload adds the block-sparse pooling and selection
 LAUNCHES_VS, LAUNCHES_BAND, LAUNCHES_MIXED = 10, 2, 12
+LAUNCHES_FLEX = 8          # two groups of 64 queries x (pass 1, combine, pass 2), plan from the block mask, attention
 
 
-def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=None):
+def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=None, flex=None):
     """Returns ``step(record) -> out`` for one layer workload with inputs resident in HBM, the event lists it
     fills and a box holding the last plan.  kind: "vs" (estimator -> plan -> attention), "band"
     (prescribed band index set -> plan -> attention) or "mixed" (per-head pattern table)."""
     from minference_b200 import _cabi
+    from minference_b200.modules.flexprefill import active_block_mask, build_block_mask_plan
     from minference_b200.modules.minference_forward import (BLOCK_SPARSE_TOPK, LayerPattern, build_vertical_slash_plan_into,
                                                             vertical_slash_estimate)
     from minference_b200.ops.block_sparse_flash_attention import build_block_sparse_plan
@@ -292,6 +310,14 @@ def layer_runner(n, hq, hkv, vsize, ssize, dev, seed, kind, q=None, k=None, v=No
         elif kind == "band":
             e1.record()
             plan = build_vertical_slash_plan(*box["indices"], n)
+            e2.record()
+            out = sparse_attention_forward(q, k, v, plan)
+        elif kind == "flex":     # the calls flexprefill_forward makes
+            bs = flex.get("block_size", 128)
+            box["block_mask"] = active_block_mask(q, k, bs, flex["gamma"], -(-flex.get("min_budget", 1) // bs),
+                                                  -(-flex.get("max_budget", 2147483647) // bs), flex["tau"])
+            e1.record()
+            plan = build_block_mask_plan(box["block_mask"], n, bs)
             e2.record()
             out = sparse_attention_forward(q, k, v, plan)
         else:
@@ -352,6 +378,7 @@ def run_gpu_arm(args, wl):
 
     from minference_b200 import _cabi
     from minference_b200.cuda import set_status_checks
+    from minference_b200.modules.flexprefill import flexprefill_forward
     from minference_b200.modules.minference_forward import minference_prefill_forward
     from minference_b200.ops.pit_sparse_flash_attention_v2 import vertical_slash_sparse_attention
 
@@ -368,9 +395,10 @@ def run_gpu_arm(args, wl):
 
     mixed = wl in MIXED_WORKLOADS
     band = wl in LOCAL_WORKLOADS
+    flex = FLEX_PARAMS.get(wl)
     step_resident, events, box, (q, k, v) = layer_runner(n, hq, hkv, vsize, ssize, dev, rank,
                                                          "mixed" if mixed else "scattered" if wl in SCATTERED_WORKLOADS
-                                                         else "band" if band else "vs")
+                                                         else "band" if band else "flex" if flex else "vs", flex=flex)
     kinds = box["kinds"]
     table = box["table"] if mixed else {str(h): ["vertical_and_slash", vsize, ssize, 1.0] for h in range(hq)}
     cfg = {"attn_forward_config": {"best_pattern": [table]}, "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None}
@@ -415,6 +443,8 @@ def run_gpu_arm(args, wl):
     freed = [torch.cuda.Event() for _ in range(2)]
 
     def public_call(qd, kd, vd):
+        if flex:
+            return flexprefill_forward(qd, kd, vd, {"attn_forward_config": flex})
         if band:
             return vertical_slash_sparse_attention(qd, kd, vd, *box["indices"])
         return minference_prefill_forward(qd, kd, vd, cfg)
@@ -456,10 +486,12 @@ def run_gpu_arm(args, wl):
     # ---- parity of this very output at the benchmark's size: sampled row blocks of every head against an fp32
     # masked-dense recomputation over the identical index set (vertical-slash workloads)
     parity = None
-    if not mixed:
+    if flex:
+        parity = flex_parity_probe(q, k, v, out_res, box["block_mask"], flex.get("block_size", 128), n, hq, hkv)
+    elif not mixed:
         parity = vs_parity_probe(q, k, v, out_res, box["plan"], n, hq, hkv, dev)
-        if parity["max_abs"] > 2e-2 or parity["mean_abs"] > 2e-3:
-            raise SystemExit(f"parity probe failed: {parity}")
+    if parity is not None and (parity["max_abs"] > 2e-2 or parity["mean_abs"] > 2e-3):
+        raise SystemExit(f"parity probe failed: {parity}")
 
     times = torch.tensor([total_ms, e2e_ms, attn_ms], dtype=torch.float64, device=dev)
     tile_sum = torch.tensor([float(tiles)], dtype=torch.float64, device=dev)
@@ -493,7 +525,11 @@ def run_gpu_arm(args, wl):
             detail["one_gpu_1m"] = side_measurement("llama3_8b_1m_vs", dev, steps=2, warmup=1)
             torch.cuda.empty_cache()
             detail["one_gpu_1m_band"] = side_measurement("llama3_8b_1m_vs_local", dev, steps=2, warmup=1)
-        cpu_tf, cpu_desc = cpu_sample(n, hq, hkv, vsize, ssize, seed=0, budget_s=12.0, local=band)
+        if flex:
+            detail["blocks_selected_of_causal"] = float(box["block_mask"].sum().item()) / (hq * (n // 128) * (n // 128 + 1) / 2)
+            cpu_tf, cpu_desc = None, "not timed for this workload (the default workload carries the CPU baseline)"
+        else:
+            cpu_tf, cpu_desc = cpu_sample(n, hq, hkv, vsize, ssize, seed=0, budget_s=12.0, local=band)
         if mixed:
             cpu_desc = "vertical-slash heads only; " + cpu_desc
         out = {
@@ -504,7 +540,7 @@ def run_gpu_arm(args, wl):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": (hq + 2 * hkv) * n * 128 * 2,
                     "d2h_bytes_per_step": hq * n * 128 * 2, "max_abs_vs_resident_last_row": parity_probe},
-            "gpu_launches": (LAUNCHES_MIXED if mixed else LAUNCHES_BAND if band else LAUNCHES_VS) * args.steps,
+            "gpu_launches": (LAUNCHES_MIXED if mixed else LAUNCHES_BAND if band else LAUNCHES_FLEX if flex else LAUNCHES_VS) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "sparse_attn_fwd_kernel", "achieved": achieved,
                          "peak": peaks["sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["sustained"],
                          "peak_kind": f"bf16 dense sustained, of {peaks['source']}", "frac_of_burst": achieved / peaks["burst"],
@@ -552,6 +588,24 @@ def vs_parity_probe(q, k, v, out, plan, n, hq, hkv, dev, blocks_per_head=4):
         mean_sum += mean * len(picks)
         cnt += len(picks)
         del bc, bo, cc, ci
+    return {"max_abs": worst, "mean_abs": mean_sum / max(cnt, 1), "row_blocks": cnt, "heads": hq}
+
+
+def flex_parity_probe(q, k, v, out, block_mask, block, n, hq, hkv, blocks_per_head=3):
+    """Kernel output against fp32 masked-dense attention over the identical block set, sampled row blocks of every head."""
+    from minference_b200.checks import block_mask_row_block
+
+    rows = (n + 63) // 64
+    group = hq // hkv
+    worst, mean_sum, cnt = 0.0, 0.0, 0
+    for h in range(hq):
+        picks = sorted(set(sample_row_blocks(0, rows, blocks_per_head)) | {(h * 131 + 7) % rows})
+        for m in picks:
+            want = block_mask_row_block(q[0, h, 64 * m:64 * m + 64], k[0, h // group], v[0, h // group], block_mask[0, h], m, block)
+            d = (out[0, h, 64 * m:64 * m + 64].float() - want).abs()
+            worst = max(worst, d.max().item())
+            mean_sum += d.mean().item()
+            cnt += 1
     return {"max_abs": worst, "mean_abs": mean_sum / max(cnt, 1), "row_blocks": cnt, "heads": hq}
 
 

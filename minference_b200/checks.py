@@ -58,3 +58,22 @@ def compare_row_blocks(out_rows_of, q_rows_of, k, v, n_ctx: int, tables, row_blo
         total += d.sum().item()
         count += d.numel()
     return worst, total / max(count, 1)
+
+
+def block_mask_row_block(q_rows: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_mask: torch.Tensor, m: int,
+                         block: int, sm_scale: float | None = None):
+    """Attention output of row block ``m`` of one head over a block set: ``block_mask [nb, nb]`` (bool), entry (i, j)
+    set <=> query block i attends key block j, causal inside every block (the index set of the reference's
+    FlexPrefill kernel, modules/flexprefill.py:412-436).  fp32 ``[rows, D]``."""
+    dev = q_rows.device
+    rows, d = q_rows.shape
+    r0 = 64 * m
+    n_keys = min(k.shape[0], r0 + 64)
+    scale = float(sm_scale if sm_scale is not None else d ** -0.5)
+    cols = torch.arange(n_keys, device=dev)
+    rws = r0 + torch.arange(rows, device=dev)
+    mask = block_mask[r0 // block][cols // block][None, :] & (cols[None, :] <= rws[:, None])
+    s = (q_rows.float() @ k[:n_keys].float().T) * scale
+    s.masked_fill_(~mask, float("-inf"))
+    p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
+    return p @ v[:n_keys].float()
