@@ -16,9 +16,19 @@ Printed JSON (one line, rank 0):
   roofline     the attention kernel alone (CUDA events around its launch, same stream)
   cpu_baseline the CPU oracle (port of the reference's torch path) on a bounded sample
 
+  detail       what else was measured: tiles, stage times, issued over reference tiles, the parity probe of this
+               very output (sampled row blocks of every head against fp32 masked-dense attention over the
+               identical index set; the run exits non-zero above 2e-2 max / 2e-3 mean), and for the default
+               workload the band index set at the same length and the 1,048,576-token layer on this one GPU
+               (the anchor of the ring lines; --no-extras leaves these out)
+
+Workload families (--workload): *_vs (index set estimated online), *_vs_local (prescribed band), *_vs_scattered
+(prescribed scattered diagonals), *_mixed (per-head pattern table), *_flexprefill (adaptive block budgets), *_ttft*
+(whole-model prefill, metric ttft_s) and *_ring (N > 1).
+
 With N > 1 ranks (torchrun) the default workload is one 1,048,576-token sequence sharded over the
-ranks with the zigzag ring (strong scaling; K/V shards travel by NCCL send/recv); a single-GPU
-workload name with N > 1 runs replicas instead.
+ranks with the zigzag ring (strong scaling; K/V shards travel by NCCL send/recv; the line carries ring_parity,
+the band twin and issued over reference tiles); a single-GPU workload name with N > 1 runs replicas instead.
 """
 from __future__ import annotations
 
