@@ -109,13 +109,22 @@ def active_block_mask(query, key, block_size: int, gamma: float, min_budget: int
     """The block set of ``get_active_blocks`` (:953-1067) as a boolean matrix ``[B,H,nb,nb]`` on the device
     (entry (i, j): query block i attends key block j; only j <= i is set).  Budgets are in blocks.  Query head h reads
     KV head ``h // (H / Hkv)``."""
+    vertical, slash_o, last_q = last_block_scores(query, key, block_size)
+    return select_blocks(vertical, slash_o, last_q, query, key, block_size, gamma, min_budget, max_budget, tau, return_details)
+
+
+@torch.no_grad()
+def select_blocks(vertical, slash_o, last_q, query, key, block_size: int, gamma: float, min_budget: int, max_budget: int,
+                  tau: float = 0.0, return_details: bool = False):
+    """From the column means ``vertical [B,H,N]`` and diagonal means ``slash_o [B,H,N]`` (by distance from the main
+    diagonal) of the last query block to the block set: budgets, pooling, the Jensen-Shannon test, top-k and the
+    block-sparse fallback (:994-1066).  Plain torch on whatever device the tensors live on."""
     B, H, N, D = query.shape
     Hkv = key.shape[1]
     rep = H // Hkv
     dev = query.device
     nb = math.ceil(N / block_size)
     max_budget = min(max_budget, nb)
-    vertical, slash_o, last_q = last_block_scores(query, key, block_size)
     slash = slash_o.flip(-1)                                       # the reference's index j = N-1-o
     n_vert = (_score_cover_topk(vertical, gamma) // 128 + 1).clamp(min_budget, max_budget)      # :995-1000
     n_slash = (_score_cover_topk(slash, gamma) // 128 + 1).clamp(min_budget, max_budget)
@@ -131,8 +140,9 @@ def active_block_mask(query, key, block_size: int, gamma: float, min_budget: int
     n_slash = torch.where(block_sparse, torch.full_like(n_slash, min_budget), n_slash)
     vertical[..., :1] = torch.inf                                  # :1018-1019
     slash[..., -1:] = torch.inf
-    # the best n blocks per head as 0/1 rows over blocks (:1021-1046); ties: torch.topk's choice, as in the reference
-    k_max = min(int(max(n_vert.max().item(), n_slash.max().item())), nb)
+    # the best n blocks per head as 0/1 rows over blocks (:1021-1046); ties: torch.topk's choice, as in the reference.
+    # No budget exceeds max_budget, so that many candidates are enough and nothing has to be read back for it.
+    k_max = max_budget
     rank = torch.arange(k_max, device=dev)
 
     def chosen(scores, budget):
@@ -146,13 +156,19 @@ def active_block_mask(query, key, block_size: int, gamma: float, min_budget: int
     dist = ii[:, None] - ii[None, :]
     tril = dist >= 0
     mask = (sel_v[:, :, None, :] | sel_d[:, :, dist.clamp(min=0)]) & tril                       # :903-921
-    for b, h in block_sparse.nonzero().tolist():                   # :1049-1066
-        avg_q = _mean_pool_rows(query[b:b + 1, h:h + 1], block_size, False)[0, 0]
-        attn = torch.einsum("id,jd->ij", avg_q / math.sqrt(D), avg_k[b, h // rep]).masked_fill_(~tril, float("-inf"))
-        attn = torch.softmax(attn, dim=-1, dtype=torch.float32).view(-1)
-        vals, idx = torch.sort(attn, descending=True)
-        keep = idx[torch.cumsum(vals, dim=-1) <= gamma * nb]       # :886-890
-        mask[b, h].view(-1)[keep] = True
+    heads = block_sparse.view(-1).nonzero().view(-1)               # :1049-1066, all such heads of a group at once
+    if heads.numel():
+        avg_q = _mean_pool_rows(query, block_size, False).view(B * H, nb, D)
+        kv_of = (heads // H) * Hkv + (heads % H) // rep
+        flat = mask.view(B * H, nb * nb)
+        per_group = max(1, (1 << 27) // (nb * nb))                 # heads whose nb x nb score matrices fit 512 MB
+        for g0 in range(0, heads.numel(), per_group):
+            hs, ks = heads[g0:g0 + per_group], kv_of[g0:g0 + per_group]
+            attn = torch.einsum("hid,hjd->hij", avg_q[hs] / math.sqrt(D), avg_k.view(B * Hkv, nb, D)[ks])
+            attn = torch.softmax(attn.masked_fill_(~tril, float("-inf")), dim=-1, dtype=torch.float32).view(hs.numel(), -1)
+            vals, idx = torch.sort(attn, dim=-1, descending=True)
+            keep = torch.cumsum(vals, dim=-1) <= gamma * nb        # :886-890
+            flat[hs] |= torch.zeros_like(keep).scatter_(1, idx, keep)
     if return_details:
         return mask, {"n_vertical": n_vert, "n_slash": n_slash, "block_sparse": block_sparse, "js": js,
                       "vertical_pooled": vertical, "slash_pooled": slash}

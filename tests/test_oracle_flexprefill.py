@@ -58,3 +58,24 @@ def test_attention_oracle_over_a_block_set_is_causal_inside_blocks():
     assert bm.all(dim=0).all(dim=0).equal(torch.tril(torch.ones(2, 2, dtype=torch.bool)))
     assert torch.allclose(out2[:, :, :200], torch.nn.functional.scaled_dot_product_attention(
         q[:, :, :200], k[:, :, :200], v[:, :, :200], is_causal=True), atol=2e-5)
+
+
+def test_host_side_block_selection_of_the_product_matches_reference_fixtures(golden_dir):
+    """``select_blocks`` (budgets, pooling, Jensen-Shannon test, top-k, block-sparse fallback: the part of the product
+    that is plain torch) fed with the last-block scores computed in torch on CPU: the reference's block sets, bit for bit."""
+    import math
+
+    from minference_b200.modules.flexprefill import select_blocks
+
+    for path in sorted(glob.glob(os.path.join(golden_dir, "flexprefill_*.npz"))):
+        q, k, _, p, ref = fixture_case(path)
+        D = q.shape[-1]
+        kk = k.repeat_interleave(q.shape[1] // k.shape[1], 1)
+        last_q = q[:, :, -128:] / math.sqrt(D)
+        qk = torch.einsum("bhid,bhjd->bhij", last_q, kk)
+        causal = torch.arange(128)[:, None] >= torch.arange(128)[None, :]
+        qk[..., -128:].masked_fill_(~causal, float("-inf"))
+        pr = torch.softmax(qk, dim=-1, dtype=torch.float32)
+        slash_by_offset = (R.flex_sum_all_diagonal_matrix(pr) / 128).flip(-1)
+        mask = select_blocks(pr.mean(-2), slash_by_offset, last_q, q, k, 128, p["gamma"], p["min_budget"], p["max_budget"], p["tau"])
+        assert np.array_equal(mask[0].numpy(), ref), path
