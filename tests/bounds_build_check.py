@@ -36,6 +36,26 @@ def main():
         d = (out.float().cpu() - ref[:, :, :n]).abs()
         assert d.max().item() < 2e-2 and d.mean().item() < 2e-3, (n, d.max().item())
         assert int(tables[0].max()) <= s_idx.shape[2] and int(tables[2].max()) <= v_idx.shape[2]
+    # the plan from a block mask (FlexPrefill) through the same build: ragged length, the most runs a row can have
+    from minference_b200.modules.flexprefill import build_block_mask_plan, flexprefill_forward
+
+    for n, block in [(777, 128), (1000, 64), (2048 + 5, 128)]:
+        nb = -(-n // block)
+        mask = torch.eye(nb, dtype=torch.bool)
+        mask[::2, ::2] = True
+        mask = (mask & torch.tril(torch.ones(nb, nb, dtype=torch.bool)))[None, None].expand(1, 2, nb, nb).contiguous()
+        q, k, v = make_qkv(n, 2, 1, seed=n + 3, dtype=torch.bfloat16)
+        plan = build_block_mask_plan(mask.to(dev), n, block)
+        out = torch.full((1, 2, n, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+        sparse_attention_forward(q.to(dev), k.to(dev), v.to(dev), plan, out=out)
+        torch.cuda.synchronize()
+        assert plan.status.tolist()[:2] == [0, 0], (n, plan.status.tolist())
+        assert torch.isfinite(out.float()).all(), n
+        ref, _ = R.flexprefill_attention_oracle(q, k, v, 0.9, block_size=block, block_mask=mask)
+        d = (out.float().cpu() - ref[:, :, :n]).abs()
+        assert d.max().item() < 2e-2 and d.mean().item() < 2e-3, (n, d.max().item())
+    q, k, v = (t.to(dev) for t in make_qkv(1500, 4, 2, seed=9, dtype=torch.bfloat16))
+    assert torch.isfinite(flexprefill_forward(q, k, v, {"attn_forward_config": {"gamma": 0.8, "tau": 0.1}}).float()).all()
     print("BOUNDS_OK")
 
 

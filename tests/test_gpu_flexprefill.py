@@ -205,3 +205,20 @@ def test_short_sequences_are_dense_and_the_bnhd_entry_point_matches(dev):
     assert b.shape == (1, 2048, 2, 128) and torch.equal(a, b.transpose(1, 2))
     with pytest.raises(Exception):
         flexprefill_forward(q, k, v, {"attn_forward_config": {"block_size": 32}})
+
+
+def test_batch_of_two_sequences(dev):
+    """Two sequences in one call: block sets and outputs equal the per-sequence calls."""
+    from minference_b200.modules.flexprefill import active_block_mask, flexprefill_forward
+    from minference_b200.synthetic import make_qkv
+
+    n = 2048 + 64
+    a = [t.to(dev) for t in make_qkv(n, 4, 2, seed=61, dtype=torch.bfloat16)]
+    b = [t.to(dev) for t in make_qkv(n, 4, 2, seed=62, dtype=torch.bfloat16, plant=False)]
+    both = [torch.cat((x, y), dim=0) for x, y in zip(a, b)]
+    cfg = {"attn_forward_config": {"gamma": 0.7, "tau": 0.0, "max_budget": 512}}
+    out = flexprefill_forward(*both, cfg)
+    m_both = active_block_mask(both[0], both[1], 128, 0.7, 1, 4, 0.0)
+    for i, one in enumerate((a, b)):
+        assert torch.equal(m_both[i], active_block_mask(one[0], one[1], 128, 0.7, 1, 4, 0.0)[0])
+        assert torch.equal(out[i], flexprefill_forward(*one, cfg)[0])
