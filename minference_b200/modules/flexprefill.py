@@ -21,6 +21,7 @@ import math
 import torch
 
 from .. import _cabi
+from ..cuda import _status_checks_enabled
 from ..ops.sparse_forward import SparsePlan, sparse_attention_forward
 
 SUPPORTED_BLOCK_SIZES = (64, 128)
@@ -64,7 +65,8 @@ def last_block_scores(query, key, block_size: int):
         run(2, row_stats, scores[0], scores[1])
         vertical[:, :, :ctx] += scores[0]
         slash[:, :, :ctx] += scores[1]
-    _cabi.raise_on_status(status, "flexprefill estimator")
+    if _status_checks_enabled():
+        _cabi.raise_on_status(status, "flexprefill estimator")
     return vertical / block_size, slash / block_size, last_q
 
 
@@ -224,7 +226,8 @@ def _flex_bhnd(q, k, v, gamma, tau, min_budget, max_budget, softmax_scale, block
                              math.ceil(max_budget / block_size), tau)
     plan = build_block_mask_plan(mask, N, block_size)
     out = sparse_attention_forward(q, k, v, plan, sm_scale=softmax_scale)
-    _cabi.raise_on_status(plan.status, "flex_prefill_attention")
+    if _status_checks_enabled():
+        _cabi.raise_on_status(plan.status, "flex_prefill_attention")
     return out
 
 
