@@ -52,23 +52,34 @@ __global__ void __launch_bounds__(kMaskPlanWarps * 32) block_mask_plan_kernel(co
             overflow = true;
         }
     };
-    for (int j0 = 0; j0 <= i; j0 += 32) {
-        const int j = j0 + lane;
-        unsigned w = __ballot_sync(0xffffffffu, j <= i && row[j] != 0);
-        int pos = 0;                                          // bits below pos are done
-        while (pos < 32) {
-            if (run_start < 0) {
-                const unsigned rest = pos ? (w >> pos) << pos : w;
-                if (rest == 0u) break;
-                pos = __ffs(rest) - 1;
-                run_start = j0 + pos;
+    // four words of the row per round: the four loads are in flight together
+    for (int j00 = 0; j00 <= i; j00 += 128) {
+        unsigned char b4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j00 + 32 * u + lane;
+            b4[u] = j <= i ? row[j] : (unsigned char)0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j0 = j00 + 32 * u;
+            if (j0 > i) break;
+            const unsigned w = __ballot_sync(0xffffffffu, b4[u] != 0);
+            int pos = 0;                                          // bits below pos are done
+            while (pos < 32) {
+                if (run_start < 0) {
+                    const unsigned rest = pos ? (w >> pos) << pos : w;
+                    if (rest == 0u) break;
+                    pos = __ffs(rest) - 1;
+                    run_start = j0 + pos;
+                }
+                // the run goes on from bit pos: find its first zero
+                const unsigned zeros = ~w & (pos ? (0xffffffffu >> pos) << pos : 0xffffffffu);
+                if (zeros == 0u) break;                           // runs to the end of this word
+                pos = __ffs(zeros) - 1;
+                emit(run_start, j0 + pos);
+                run_start = -1;
             }
-            // the run goes on from bit pos: find its first zero
-            const unsigned zeros = ~w & (pos ? (0xffffffffu >> pos) << pos : 0xffffffffu);
-            if (zeros == 0u) break;                           // runs to the end of this word
-            pos = __ffs(zeros) - 1;
-            emit(run_start, j0 + pos);
-            run_start = -1;
         }
     }
     if (run_start >= 0) emit(run_start, i + 1);
