@@ -80,10 +80,14 @@ __device__ __forceinline__ float div_refined(float x, float d, float rcp) {
     return fmaf(fmaf(-q, d, x), rcp, q);
 }
 // The reference's logits: the bf16 GEMM output divided by sqrt(d) in fp32 and rounded to bf16 again.
+// MUL: one multiply by the reciprocal instead of the refined division.  For the two divisors the callers use,
+// sqrt(128) and 1, the bf16 result is the same for every one of the 65536 bf16 inputs (checked exhaustively on
+// the host: the quotient of an 8-bit significand never lies within an fp32 rounding error of a bf16 tie).
+template <bool MUL>
 __device__ __forceinline__ void logits_pair(uint32_t a0, uint32_t a1, float d, float rcp, float& v0, float& v1) {
     const uint32_t g = pack_bf16x2(__uint_as_float(a0), __uint_as_float(a1));
-    const uint32_t r = pack_bf16x2(div_refined(__uint_as_float(g << 16), d, rcp),
-                                   div_refined(__uint_as_float(g & 0xffff0000u), d, rcp));
+    const float x0 = __uint_as_float(g << 16), x1 = __uint_as_float(g & 0xffff0000u);
+    const uint32_t r = MUL ? pack_bf16x2(x0 * rcp, x1 * rcp) : pack_bf16x2(div_refined(x0, d, rcp), div_refined(x1, d, rcp));
     v0 = __uint_as_float(r << 16);
     v1 = __uint_as_float(r & 0xffff0000u);
 }
@@ -94,7 +98,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int PASS>
+template <int PASS, bool MUL>
 __global__ void __launch_bounds__(kEstThreads, 2)
 vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const EstArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -225,14 +229,14 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     if (plain) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
-                            logits_pair(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, x[j], x[j + 1]);
+                            logits_pair<MUL>(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, x[j], x[j + 1]);
                             mx = max3(mx, x[j], x[j + 1]);
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
                             float v0, v1;
-                            logits_pair(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, v0, v1);
+                            logits_pair<MUL>(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, v0, v1);
                             const int c = c0 + q2 * 32 + j;
                             x[j] = (row_ok && c <= qpos && l0 + q2 * 32 + j < a.n_k) ? v0 : -INFINITY;
                             x[j + 1] = (row_ok && c + 1 <= qpos && l0 + q2 * 32 + j + 1 < a.n_k) ? v1 : -INFINITY;
@@ -298,7 +302,7 @@ vs_scores_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
                             float v0, v1;
-                            logits_pair(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, v0, v1);
+                            logits_pair<MUL>(xr[j], xr[j + 1], a.sqrt_d, a.rcp_sqrt_d, v0, v1);
                             const int i0 = q2 * 32 + j;
                             const float2 cc = *reinterpret_cast<const float2*>(&ctl->cst[hh][i0]);
                             float p0 = fast_exp2(fmaf(v0, kLog2e, cc.x));
@@ -680,12 +684,18 @@ extern "C" int minf_vs_scores_pass_divisor(
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t smem = kEstCtlOff + sizeof(EstControl);
     dim3 grid(blocks, hkv * a.pairs_per_group, batch);
+    // the reciprocal multiply is exact for these two divisors (see logits_pair); any other one takes the division
+    const bool mul = logit_divisor == 1.0f || logit_divisor == sqrtf(128.0f);
+    auto launch = [&](auto kernel) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kEstThreads, smem, st>>>(tq, tk, a);
+        return cudaSuccess;
+    };
     if (pass == 1) {
-        MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        vs_scores_kernel<1><<<grid, kEstThreads, smem, st>>>(tq, tk, a);
+        MINF_CUDA_OK(mul ? launch(vs_scores_kernel<1, true>) : launch(vs_scores_kernel<1, false>));
     } else {
-        MINF_CUDA_OK(cudaFuncSetAttribute(vs_scores_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        vs_scores_kernel<2><<<grid, kEstThreads, smem, st>>>(tq, tk, a);
+        MINF_CUDA_OK(mul ? launch(vs_scores_kernel<2, true>) : launch(vs_scores_kernel<2, false>));
     }
     MINF_LAUNCH_OK("vs_scores_kernel");
     return MINF_OK;
