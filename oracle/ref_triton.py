@@ -20,6 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CUBIN = os.path.join(HERE, "_ref", "ref_triton_vs_fwd.cubin")
 CUBIN_BLOCK_SPARSE = os.path.join(HERE, "_ref", "ref_triton_bs_fwd.cubin")
 CUBIN_128K_8HEADS = os.path.join(HERE, "_ref", "ref_triton_vs_fwd_128k_8heads.cubin")   # specialised like a JIT call
+CUBIN_FLEX = os.path.join(HERE, "_ref", "ref_triton_flex_fwd.cubin")       # modules/flexprefill.py:352-495, 128-token blocks
 
 _CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
 
@@ -74,7 +75,8 @@ class ReferenceTritonKernel:
         holders += [ctypes.c_void_p(0), ctypes.c_void_p(0)]       # global / profile scratch: sizes are 0 for these kernels
         argv = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        self._ok(self.cu.cuLaunchKernel(self.func, int(grid[0]), int(grid[1]), 1, 32 * int(self.meta["num_warps"]), 1, 1,
+        self._ok(self.cu.cuLaunchKernel(self.func, int(grid[0]), int(grid[1]), int(grid[2]) if len(grid) > 2 else 1,
+                                        32 * int(self.meta["num_warps"]), 1, 1,
                                         int(self.meta["shared"]), stream, argv, None), "cuLaunchKernel")
 
     def __call__(self, q, k, v, seqlens, block_count, block_offset, column_count, column_index, sm_scale):
@@ -116,6 +118,47 @@ def reference_block_sparse_attention(kernel: ReferenceTritonKernel, q, k, v, blo
     out = kernel.launch(qp, kp, vp, D ** -0.5, {"seqlens": seqlens, "block_index": block_index.contiguous()},
                         {"NUM_ROWS": block_index.shape[-2], "MAX_BLOCKS_PRE_ROW": block_index.shape[-1]})
     return out[:, :, :N]
+
+
+def reference_flex_block_attention(kernel: ReferenceTritonKernel, q, k, v, block_mask, block_size: int = 128,
+                                   softmax_scale: float | None = None):
+    """The reference's ``triton_block_wise_prefill_attention`` (modules/flexprefill.py:495-616) around its own kernel
+    (:352-495): tensors in ``[B,N,H,D]`` layout, the block set as sorted flattened ids ``i*nb + j`` padded with
+    ``nb*(nb+1)`` (:536-541), the per-row bins as counts + cumulative sum (the torch form of :312-350 given in the
+    reference's comment), ``softmax_scale * log2(e)`` (:545-548), grid ``(B, H, nb)``.  ``q [B,H,N,128]``,
+    ``k, v [B,Hkv,N,128]`` bf16 and ``block_mask [B,H,nb,nb]`` bool on the device; returns ``[B,H,N,128]``."""
+    import math
+
+    assert block_size == 128, "the binary was built for 128-token blocks"
+    B, H, N, D = q.shape
+    Hkv = k.shape[1]
+    nb = (N + block_size - 1) // block_size
+    qb, kb, vb = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    ob = torch.zeros_like(qb)
+    lower = torch.tril(block_mask.to(torch.bool))
+    counts = lower.sum(-1)                                                    # [B,H,nb]
+    bins = torch.nn.functional.pad(torch.cumsum(counts, -1), (1, 0)).to(torch.int32).contiguous()
+    width = int(counts.sum(-1).max().item())
+    ids = torch.full((B, H, width), nb * (nb + 1), dtype=torch.int64, device=q.device)
+    for b in range(B):
+        for h in range(H):
+            flat = lower[b, h].reshape(-1).nonzero().view(-1)               # row-major order = ascending ids
+            ids[b, h, :flat.numel()] = flat
+    scale = (1.0 / math.sqrt(D) if softmax_scale is None else softmax_scale) * math.log2(math.e)
+    values = {"q_ptr": qb.data_ptr(), "k_ptr": kb.data_ptr(), "v_ptr": vb.data_ptr(), "o_ptr": ob.data_ptr(),
+              "block_idx_ptr": ids.data_ptr(), "idx_bin_ptr": bins.data_ptr(), "BATCH_SIZE": B, "NUM_HEADS": H,
+              "NUM_KV_HEADS": Hkv, "GQA_GROUPS": H // Hkv, "Q_LEN": N, "K_LEN": N, "NUM_BLOCK": nb, "grid_offset": 0,
+              "softmax_scale": scale}
+    for name, t in (("q", qb), ("k", kb), ("v", vb), ("o", ob)):
+        for axis, st in zip("bnhd", t.stride()):
+            values[f"stride_{name}{axis}"] = st
+    for axis, st in zip(("bb", "bh", "bt"), ids.stride()):
+        values["stride_" + axis] = st
+    for axis, st in zip(("ib", "ih", "it"), bins.stride()):
+        values["stride_" + axis] = st
+    kernel.launch_raw(values, (B, H, nb))
+    torch.cuda.synchronize()
+    return ob.transpose(1, 2)
 
 
 def streaming_available() -> bool:

@@ -222,3 +222,29 @@ def test_batch_of_two_sequences(dev):
     for i, one in enumerate((a, b)):
         assert torch.equal(m_both[i], active_block_mask(one[0], one[1], 128, 0.7, 1, 4, 0.0)[0])
         assert torch.equal(out[i], flexprefill_forward(*one, cfg)[0])
+
+
+@pytest.mark.parametrize("n,heads,kv_heads", [(2048, 4, 2), (4096 + 100, 2, 1), (1500, 4, 4)])
+def test_attention_over_a_block_set_matches_reference_triton_kernel_on_gpu(dev, n, heads, kv_heads):
+    """The reference's own block-wise prefill kernel (modules/flexprefill.py:352-495, compiled ahead of time for
+    sm_100a by oracle/build_ref.py) and this library's kernel on the same inputs and the same block set: a random one
+    and the one the adaptive selection returns."""
+    from minference_b200.modules.flexprefill import active_block_mask, build_block_mask_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import make_qkv
+    from oracle import ref_triton
+
+    if not ref_triton.available(ref_triton.CUBIN_FLEX):
+        pytest.skip("the reference kernel binary is not built (oracle/build_ref.py --triton)")
+    kernel = ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_FLEX)
+    q, k, v = (t.to(dev) for t in make_qkv(n, heads, kv_heads, seed=n + 7, dtype=torch.bfloat16))
+    nb = math.ceil(n / 128)
+    masks = [_random_block_mask(nb, heads, 0.3, seed=n + 2).to(dev),
+             active_block_mask(q, k, 128, 0.8, 1, 8, 0.0)]
+    for mask in masks:
+        plan = build_block_mask_plan(mask, n, 128)
+        got = sparse_attention_forward(q, k, v, plan).float()
+        want = ref_triton.reference_flex_block_attention(kernel, q, k, v, mask).float()
+        d = (got - want).abs()
+        assert plan.status.tolist()[:2] == [0, 0]
+        assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (n, d.max().item(), d.mean().item())
