@@ -5,7 +5,8 @@
 (ops/block_sparse_flash_attention.py:29-112) of the reference ahead of time into ``oracle/_ref``;
 this module loads those binaries through the CUDA driver API and launches them the way the
 reference's launchers do (grid ``(ceil(N/64), B*H)``, 128 threads, the argument order of the kernel
-signature: v2 :156-192, block-sparse :115-148).
+signature: v2 :156-192, block-sparse :115-148).  The streaming kernel's stage variants and the block-wise
+prefill kernel of ``modules/flexprefill.py`` (:352-495) are built and launched the same way.
 The GPU parity tests compare the product kernel with its output.  Nothing here is used by the library.
 """
 from __future__ import annotations
