@@ -122,7 +122,7 @@ def reference_block_sparse_attention(kernel: ReferenceTritonKernel, q, k, v, blo
 
 
 def reference_flex_block_attention(kernel: ReferenceTritonKernel, q, k, v, block_mask, block_size: int = 128,
-                                   softmax_scale: float | None = None):
+                                   softmax_scale: float | None = None, prepared_call: bool = False):
     """The reference's ``triton_block_wise_prefill_attention`` (modules/flexprefill.py:495-616) around its own kernel
     (:352-495): tensors in ``[B,N,H,D]`` layout, the block set as sorted flattened ids ``i*nb + j`` padded with
     ``nb*(nb+1)`` (:536-541), the per-row bins as counts + cumulative sum (the torch form of :312-350 given in the
@@ -157,7 +157,11 @@ def reference_flex_block_attention(kernel: ReferenceTritonKernel, q, k, v, block
         values["stride_" + axis] = st
     for axis, st in zip(("ib", "ih", "it"), bins.stride()):
         values["stride_" + axis] = st
-    kernel.launch_raw(values, (B, H, nb))
+    launch = lambda: kernel.launch_raw(values, (B, H, nb))
+    if prepared_call:
+        # the launch alone (for timing) and the tensors it reads and writes, which must stay alive around it
+        return launch, ob.transpose(1, 2), (qb, kb, vb, ids, bins)
+    launch()
     torch.cuda.synchronize()
     return ob.transpose(1, 2)
 

@@ -248,3 +248,44 @@ def test_attention_over_a_block_set_matches_reference_triton_kernel_on_gpu(dev, 
         d = (got - want).abs()
         assert plan.status.tolist()[:2] == [0, 0]
         assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS, (n, d.max().item(), d.mean().item())
+
+
+def test_reference_block_wise_kernel_timing_131072(dev, capsys):
+    """131072 tokens, 8 query / 2 KV heads, the block set of the adaptive selection with budgets of 64 blocks: the
+    reference's block-wise kernel and this library's kernel on the same inputs, CUDA-event times of the launches alone
+    (run with -s to see them)."""
+    from minference_b200.modules.flexprefill import active_block_mask, build_block_mask_plan
+    from minference_b200.ops.sparse_forward import sparse_attention_forward
+    from minference_b200.synthetic import make_qkv
+    from oracle import ref_triton
+
+    if not ref_triton.available(ref_triton.CUBIN_FLEX):
+        pytest.skip("the reference kernel binary is not built (oracle/build_ref.py --triton)")
+    n, hq, hkv = 131072, 8, 2
+    q, k, v = make_qkv(n, hq, hkv, seed=0, dtype=torch.bfloat16, device=dev)
+    mask = active_block_mask(q, k, 128, 0.9, 1, 64, 0.0)
+    plan = build_block_mask_plan(mask, n, 128)
+    kernel = ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_FLEX)
+    launch, ref_out, keep = ref_triton.reference_flex_block_attention(kernel, q, k, v, mask, prepared_call=True)
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), out
+
+    t_ref, _ = timed(launch)
+    t_new, out = timed(lambda: sparse_attention_forward(q, k, v, plan))
+    tiles = plan.count_tiles()
+    d = (out.float() - ref_out.float()).abs()
+    with capsys.disabled():
+        print(f"\n131072 tokens, {hq}/{hkv} heads, {int(mask.sum())} blocks of 128 ({tiles} 64x64 tiles): reference block-wise "
+              f"kernel {t_ref:.1f} ms ({tiles * 2097152 / t_ref / 1e9:.0f} TFLOP/s), product kernel {t_new:.1f} ms "
+              f"({tiles * 2097152 / t_new / 1e9:.0f} TFLOP/s), ratio {t_ref / t_new:.2f}; max-abs difference {d.max().item():.2e}")
+    del keep
+    assert d.max().item() < MAX_ABS and d.mean().item() < MEAN_ABS
+    assert t_new < t_ref
