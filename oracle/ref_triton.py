@@ -22,6 +22,7 @@ CUBIN = os.path.join(HERE, "_ref", "ref_triton_vs_fwd.cubin")
 CUBIN_BLOCK_SPARSE = os.path.join(HERE, "_ref", "ref_triton_bs_fwd.cubin")
 CUBIN_128K_8HEADS = os.path.join(HERE, "_ref", "ref_triton_vs_fwd_128k_8heads.cubin")   # specialised like a JIT call
 CUBIN_FLEX = os.path.join(HERE, "_ref", "ref_triton_flex_fwd.cubin")       # modules/flexprefill.py:352-495, 128-token blocks
+CUBIN_FLEX_128K_8HEADS = os.path.join(HERE, "_ref", "ref_triton_flex_fwd_128k_8heads.cubin")   # specialised like a JIT call
 
 _CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES = 8
 

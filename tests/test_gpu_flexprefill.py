@@ -265,7 +265,9 @@ def test_reference_block_wise_kernel_timing_131072(dev, capsys):
     q, k, v = make_qkv(n, hq, hkv, seed=0, dtype=torch.bfloat16, device=dev)
     mask = active_block_mask(q, k, 128, 0.9, 1, 64, 0.0)
     plan = build_block_mask_plan(mask, n, 128)
-    kernel = ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_FLEX)
+    # the build specialised for exactly these sizes (what the JIT does: unit strides folded, divisibility hints)
+    kernel = ref_triton.ReferenceTritonKernel(ref_triton.CUBIN_FLEX_128K_8HEADS if ref_triton.available(ref_triton.CUBIN_FLEX_128K_8HEADS)
+                                              else ref_triton.CUBIN_FLEX)
     launch, ref_out, keep = ref_triton.reference_flex_block_attention(kernel, q, k, v, mask, prepared_call=True)
 
     def timed(fn):
