@@ -243,6 +243,48 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
                 // new range is the next start, and only the lanes after it are tested again: one ballot per range
                 // instead of one shuffle pair per candidate.
                 unsigned todo = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
+                // Scattered lists: every candidate of the batch opens a range of its own.  Lane l then knows the
+                // range it closes without waiting for the others -- it starts at the previous candidate's tile --
+                // so the whole batch is written with one store per lane and its columns are marked in one sweep.
+                const unsigned all_valid = __ballot_sync(0xffffffffu, valid);    // lanes 0..cnt-1
+                const int cnt = __popc(all_valid);
+                if (todo == all_valid && cnt > 1) {
+                    int ef = __shfl_up_sync(0xffffffffu, e, 1);
+                    if (lane == 0) ef = e_first;
+                    const int re_l = ef + ((prev - ef + 63) & ~63);
+                    if (__ballot_sync(0xffffffffu, valid && e > re_l + 64) == all_valid) {
+                        const int rs_l = valid ? ef - 64 : INT_MAX, re_v = valid ? re_l : INT_MAX;
+                        if (valid && MINF_IN_BOUNDS(a.status, nrng + lane < min(a.cap_s, a.rb_base + m + 2) && rs_l >= 0 && re_l > rs_l))
+                            rng[nrng + lane] = make_int2(rs_l, re_l);
+                        nrng += cnt;
+                        const int re_last = __shfl_sync(0xffffffffu, re_l, cnt - 1);
+                        e_first = __shfl_sync(0xffffffffu, e, cnt - 1);
+                        for (;;) {          // columns up to the end of the batch: gathered unless a range covers them
+                            const int i = vp + lane;
+                            const int val = i < nnz_v ? v_list[i] : INT_MAX;
+                            const bool in_batch = val < re_last;
+                            int blo = 0, bhi = cnt;                     // number of ranges of the batch starting at or below val
+#pragma unroll
+                            for (int it = 0; it < 6; ++it) {
+                                const int mid = (blo + bhi) >> 1;
+                                const int rs_mid = __shfl_sync(0xffffffffu, rs_l, mid & 31);
+                                if (blo < bhi) { if (rs_mid <= val) blo = mid + 1; else bhi = mid; }
+                            }
+                            const int re_before = __shfl_sync(0xffffffffu, re_v, max(blo - 1, 0));
+                            const bool covered = blo > 0 && val < re_before;
+                            const unsigned marks = __ballot_sync(0xffffffffu, in_batch && !covered);
+                            const int n_in = __popc(__ballot_sync(0xffffffffu, in_batch));
+                            if (marks && lane == 0) {
+                                const int w0 = vp >> 5, sh = vp & 31;
+                                if (MINF_IN_BOUNDS(a.status, w0 < words_v)) wb[w0] |= marks << sh;
+                                if (sh && (marks >> (32 - sh)) && MINF_IN_BOUNDS(a.status, w0 + 1 < words_v)) wb[w0 + 1] |= marks >> (32 - sh);
+                            }
+                            vp += n_in;
+                            if (n_in < 32) break;
+                        }
+                        todo = 0u;
+                    }
+                }
                 while (todo) {
                     const int re_mine = e_first + ((prev - e_first + 63) & ~63);
                     const unsigned opens = __ballot_sync(0xffffffffu, ((todo >> lane) & 1u) && e > re_mine + 64);
