@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
     __shared__ uint32_t sh_prefix, sh_remaining;
     __shared__ int warp_cnt[8];
     __shared__ int sh_base, sh_ties;
-    __shared__ unsigned char take_flag[256];
+    __shared__ unsigned take_word[8];
 
     const int m_loc = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int m = a.m_base + m_loc;           // position of the query block in the sequence
@@ -112,8 +112,15 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
         for (int shift = 24; shift >= 0; shift -= 8) {
             hist[threadIdx.x] = 0;
             __syncthreads();
-            for (int n = threadIdx.x; n < n_blocks; n += blockDim.x)
-                if ((keys[n] & prefix_mask) == prefix) atomicAdd(&hist[(keys[n] >> shift) & 255u], 1u);
+            // scores of one head lie close together, so most keys of a warp share the digit: one shared-memory
+            // atomic per distinct digit of the warp instead of one per key
+            for (int base = warp * 32; base < n_blocks; base += 256) {
+                const int n = base + lane;
+                const bool act = n < n_blocks && (keys[n] & prefix_mask) == prefix;
+                const uint32_t digit = act ? (keys[n] >> shift) & 255u : 0xffffffffu;
+                const unsigned peers = __match_any_sync(0xffffffffu, digit);
+                if (act && lane == __ffs(peers) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
+            }
             __syncthreads();
             if (threadIdx.x == 0) {
                 uint32_t rem = remaining;
@@ -163,19 +170,25 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
         int round_take = 0;
         for (int w = 0; w < 8; ++w) { if (w < warp) dst += warp_cnt[w]; round_take += warp_cnt[w]; }
         if (take && bi) bi[dst] = n;
-        take_flag[threadIdx.x] = take ? 1 : 0;   // staged so thread 0 can merge adjacent blocks into ranges
+        if (lane == 0) take_word[warp] = kb;     // staged so thread 0 can merge adjacent blocks into ranges
         __syncthreads();
         if (threadIdx.x == 0) {
             sh_base += round_take;
             sh_ties += round_ties;
             if (rng) {
-                const int hi = min(start + 256, n_blocks);
-                for (int n2 = start; n2 < hi; ++n2) {
-                    if (!take_flag[n2 - start]) continue;
-                    if (n2 * 64 == cur_hi) cur_hi += 64;
-                    else {
-                        if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
-                        cur_lo = n2 * 64; cur_hi = cur_lo + 64;
+                for (int w = 0; w < 8; ++w) {    // runs of ones, cut out of the ballot words with bit scans
+                    unsigned word = take_word[w];
+                    while (word) {
+                        const int lo = __ffs(word) - 1;
+                        const unsigned inv = ~(word >> lo);
+                        const int len = inv ? __ffs(inv) - 1 : 32 - lo;
+                        const int first = (start + 32 * w + lo) * 64;
+                        if (first == cur_hi) cur_hi += 64 * len;
+                        else {
+                            if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
+                            cur_lo = first; cur_hi = first + 64 * len;
+                        }
+                        word = lo + len >= 32 ? 0u : word & ~((1u << (lo + len)) - 1u);
                     }
                 }
             }
