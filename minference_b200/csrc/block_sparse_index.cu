@@ -66,9 +66,10 @@ struct BsSelectArgs {
     PlanLayout layout;
     int m_base;              // query block of blockIdx.x = 0 (sequence-sharded callers plan a window of query blocks)
     int rows_q;              // query blocks held by qpool per head (rows_pad for a whole sequence)
+    int rows_per_cta;        // 8, or 4 when eight rows of keys do not fit shared memory
 };
 
-constexpr int kBsRows = 4;     // query blocks per CTA: every pooled key row is fetched once for all of them
+constexpr int kBsRowsMax = 8;  // query blocks per CTA (4 or 8: what fits shared memory), one warp each in the select phase
 
 // order-preserving map of a bf16 value (held in a float) to 16 bits: negative values have all bits flipped,
 // the others the sign bit set, so unsigned comparison of the keys is comparison of the values
@@ -78,40 +79,37 @@ __device__ __forceinline__ uint32_t bf16_key(float x) {
 }
 
 __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
-    extern __shared__ uint16_t keys16[];      // [kBsRows][rows_pad] score keys
-    __shared__ float qv[kBsRows][128];
-    __shared__ uint32_t hist[256];
-    __shared__ uint32_t sh_prefix, sh_remaining;
-    __shared__ int warp_cnt[8];
-    __shared__ int sh_base, sh_ties;
-    __shared__ unsigned take_word[8];
+    extern __shared__ uint16_t keys16[];      // [rows_per_cta][rows_pad] score keys
+    __shared__ float qv[4][128];
+    __shared__ uint32_t hist[8][256];         // one histogram per warp
 
     const int h = blockIdx.y, b = blockIdx.z;
     if (a.head_select && a.head_select[h] == 0) return;
     const int hk = h / (a.hq / a.hkv);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t bh = (size_t)b * a.hq + h;
-    const int m_loc0 = blockIdx.x * kBsRows;                  // first query block of this CTA (inside qpool / the plan)
-    const int nr = min(kBsRows, a.rows_q - m_loc0);
+    const int m_loc0 = blockIdx.x * a.rows_per_cta;           // first query block of this CTA (inside qpool / the plan)
+    const int nr = min(a.rows_per_cta, a.rows_q - m_loc0);
 
-    for (int i = threadIdx.x; i < kBsRows * 128; i += 256) {
-        const int r = i >> 7;
-        qv[r][i & 127] = r < nr ? __bfloat162float(a.qpool[(bh * a.rows_q + m_loc0 + r) * 128 + (i & 127)]) : 0.f;
-    }
-    __syncthreads();
-
-    // ---- scores of key blocks 0..m of the CTA's last query block against all its query blocks: four key blocks per
-    // warp step, eight lanes (16 of the 128 dimensions each) per key block; fp32 dot products rounded to bf16 like the
-    // reference's bf16 einsum
-    {
-        const int n_max = a.m_base + m_loc0 + nr;
+    // ---- scores, four query blocks at a time: key blocks 0..m of the last of them against all four; four key blocks
+    // per warp step, eight lanes (16 of the 128 dimensions each) per key block; fp32 dot products rounded to bf16 like
+    // the reference's bf16 einsum.  Every pooled key row is fetched once per four query blocks.
+    const __nv_bfloat16* kp = a.kpool + ((size_t)b * a.hkv + hk) * a.rows_pad * 128;
+    for (int r0 = 0; r0 < nr; r0 += 4) {
+        const int nq = min(4, nr - r0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < 4 * 128; i += 256) {
+            const int r = i >> 7;
+            qv[r][i & 127] = r < nq ? __bfloat162float(a.qpool[(bh * a.rows_q + m_loc0 + r0 + r) * 128 + (i & 127)]) : 0.f;
+        }
+        __syncthreads();
+        const int n_max = a.m_base + m_loc0 + r0 + nq;
         const int sub = lane >> 3, part = lane & 7;
-        float q[kBsRows][16];
+        float q[4][16];
 #pragma unroll
-        for (int r = 0; r < kBsRows; ++r)
+        for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int i = 0; i < 16; ++i) q[r][i] = qv[r][16 * part + i];
-        const __nv_bfloat16* kp = a.kpool + ((size_t)b * a.hkv + hk) * a.rows_pad * 128;
         for (int n0 = warp * 4; n0 < n_max; n0 += 32) {
             const int n = n0 + sub;
             uint4 raw[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
@@ -121,142 +119,142 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
                 raw[1] = src[1];
             }
             const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(raw);
-            float s[kBsRows];
-#pragma unroll
-            for (int r = 0; r < kBsRows; ++r) s[r] = 0.f;
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float2 kf = __bfloat1622float2(k2[i]);
 #pragma unroll
-                for (int r = 0; r < kBsRows; ++r) s[r] = fmaf(q[r][2 * i + 1], kf.y, fmaf(q[r][2 * i], kf.x, s[r]));
+                for (int r = 0; r < 4; ++r) s[r] = fmaf(q[r][2 * i + 1], kf.y, fmaf(q[r][2 * i], kf.x, s[r]));
             }
 #pragma unroll
-            for (int r = 0; r < kBsRows; ++r) {
+            for (int r = 0; r < 4; ++r) {
                 s[r] += __shfl_xor_sync(0xffffffffu, s[r], 4);
                 s[r] += __shfl_xor_sync(0xffffffffu, s[r], 2);
                 s[r] += __shfl_xor_sync(0xffffffffu, s[r], 1);
             }
             if (part == 0 && n < n_max) {
 #pragma unroll
-                for (int r = 0; r < kBsRows; ++r)
-                    if (r < nr) keys16[(size_t)r * a.rows_pad + n] = (uint16_t)bf16_key(__bfloat162float(__float2bfloat16_rn(s[r])));
+                for (int r = 0; r < 4; ++r)
+                    if (r < nq) keys16[(size_t)(r0 + r) * a.rows_pad + n] = (uint16_t)bf16_key(__bfloat162float(__float2bfloat16_rn(s[r])));
             }
         }
     }
     __syncthreads();
 
-    for (int r = 0; r < nr; ++r) {
-        const int m_loc = m_loc0 + r;
-        const int m = a.m_base + m_loc;           // position of the query block in the sequence
-        const int n_blocks = m + 1;               // causal key blocks 0..m
-        const int k = min(a.top_k, n_blocks);     // blocks the attention kernel consumes (:81)
-        const uint16_t* keys = keys16 + (size_t)r * a.rows_pad;
+    // ---- selection: warp r takes query block r; nothing below synchronises across warps
+    const int r = warp;
+    if (r >= nr) return;
+    const int m_loc = m_loc0 + r;
+    const int m = a.m_base + m_loc;           // position of the query block in the sequence
+    const int n_blocks = m + 1;               // causal key blocks 0..m
+    const int k = min(a.top_k, n_blocks);     // blocks the attention kernel consumes (:81)
+    const uint16_t* keys = keys16 + (size_t)r * a.rows_pad;
+    uint32_t* myhist = hist[warp];
+    const unsigned lt = (1u << lane) - 1u;
 
-        uint32_t thr = 0;
-        int ties_needed = 0;
-        if (k < n_blocks) {
-            uint32_t prefix = 0, prefix_mask = 0, remaining = k;
-            for (int shift = 8; shift >= 0; shift -= 8) {
-                hist[threadIdx.x] = 0;
-                __syncthreads();
-                // scores of one head lie close together, so most keys of a warp share the digit: one shared-memory
-                // atomic per distinct digit of the warp instead of one per key
-                for (int base = warp * 32; base < n_blocks; base += 256) {
-                    const int n = base + lane;
-                    const bool act = n < n_blocks && ((uint32_t)keys[n] & prefix_mask) == prefix;
-                    const uint32_t digit = act ? ((uint32_t)keys[n] >> shift) & 255u : 0xffffffffu;
-                    const unsigned peers = __match_any_sync(0xffffffffu, digit);
-                    if (act && lane == __ffs(peers) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(peers));
-                }
-                __syncthreads();
-                if (threadIdx.x == 0) {
-                    uint32_t rem = remaining;
-                    int d = 255;
-                    for (; d > 0; --d) {
-                        if (hist[d] >= rem) break;
-                        rem -= hist[d];
-                    }
-                    sh_prefix = prefix | ((uint32_t)d << shift);
-                    sh_remaining = rem;
-                }
-                __syncthreads();
-                prefix = sh_prefix;
-                remaining = sh_remaining;
-                prefix_mask |= 255u << shift;
-                __syncthreads();
+    uint32_t thr = 0;
+    int ties_needed = 0;
+    if (k < n_blocks) {                       // radix select of the k-th largest key, two 8-bit digits
+        uint32_t prefix = 0, prefix_mask = 0, remaining = k;
+        for (int shift = 8; shift >= 0; shift -= 8) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) myhist[8 * lane + i] = 0u;
+            __syncwarp();
+            // scores of one head lie close together, so most keys of a warp step share the digit: one
+            // shared-memory atomic per distinct digit instead of one per key
+            for (int base = 0; base < n_blocks; base += 32) {
+                const int n = base + lane;
+                const bool act = n < n_blocks && ((uint32_t)keys[n] & prefix_mask) == prefix;
+                const uint32_t digit = act ? ((uint32_t)keys[n] >> shift) & 255u : 0xffffffffu;
+                const unsigned peers = __match_any_sync(0xffffffffu, digit);
+                if (act && lane == __ffs(peers) - 1) atomicAdd(&myhist[digit], (uint32_t)__popc(peers));
             }
-            thr = prefix;
-            ties_needed = (int)remaining;
-        }
-
-        // ordered compaction of the selected block ids (ascending), 256 candidates per round
-        int32_t* bi = a.block_index ? a.block_index + (bh * a.rows_pad + m) * a.top_k : nullptr;
-        int2* rng = nullptr;
-        if (a.plan && m < a.rows)
-            rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_offset(a.layout, m_loc);
-        if (threadIdx.x == 0) { sh_base = 0; sh_ties = 0; }
-        __syncthreads();
-        int nrng = 0;          // maintained by thread 0 only
-        int cur_lo = -1, cur_hi = -1;
-        for (int start = 0; start < n_blocks; start += 256) {
-            const int n = start + threadIdx.x;
-            const bool in = n < n_blocks;
-            const uint32_t key = in ? keys[n] : 0u;
-            const bool tie = in && k < n_blocks && key == thr;
-            const unsigned tb = __ballot_sync(0xffffffffu, tie);
-            if (lane == 0) warp_cnt[warp] = __popc(tb);
-            __syncthreads();
-            int tie_rank = sh_ties + __popc(tb & ((1u << lane) - 1u));
-            int round_ties = 0;
-            for (int w = 0; w < 8; ++w) { if (w < warp) tie_rank += warp_cnt[w]; round_ties += warp_cnt[w]; }
-            __syncthreads();
-            const bool take = in && (k >= n_blocks || key > thr || (tie && tie_rank < ties_needed));
-            const unsigned kb = __ballot_sync(0xffffffffu, take);
-            if (lane == 0) warp_cnt[warp] = __popc(kb);
-            __syncthreads();
-            int dst = sh_base + __popc(kb & ((1u << lane) - 1u));
-            int round_take = 0;
-            for (int w = 0; w < 8; ++w) { if (w < warp) dst += warp_cnt[w]; round_take += warp_cnt[w]; }
-            if (take && bi) bi[dst] = n;
-            if (lane == 0) take_word[warp] = kb;     // staged so thread 0 can merge adjacent blocks into ranges
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                sh_base += round_take;
-                sh_ties += round_ties;
-                if (rng) {
-                    for (int w = 0; w < 8; ++w) {    // runs of ones, cut out of the ballot words with bit scans
-                        unsigned word = take_word[w];
-                        while (word) {
-                            const int lo = __ffs(word) - 1;
-                            const unsigned inv = ~(word >> lo);
-                            const int len = inv ? __ffs(inv) - 1 : 32 - lo;
-                            const int first = (start + 32 * w + lo) * 64;
-                            if (first == cur_hi) cur_hi += 64 * len;
-                            else {
-                                if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
-                                cur_lo = first; cur_hi = first + 64 * len;
-                            }
-                            word = lo + len >= 32 ? 0u : word & ~((1u << (lo + len)) - 1u);
-                        }
-                    }
+            __syncwarp();
+            // the highest digit at which the count from the top reaches `remaining`: lane l holds digits 8l..8l+7
+            uint32_t c[8], mine = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { c[i] = myhist[8 * lane + i]; mine += c[i]; }
+            uint32_t above = mine;            // inclusive suffix sum over lanes, then made exclusive
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_down_sync(0xffffffffu, above, o);
+                if (lane + o < 32) above += t;
+            }
+            above -= mine;
+            const bool here = above < remaining && remaining <= above + mine;
+            const unsigned where = __ballot_sync(0xffffffffu, here);
+            int d = 0;
+            uint32_t rem = remaining;
+            if (here) {
+                uint32_t cum = above;
+                d = 8 * lane;
+                rem = remaining - above;
+#pragma unroll
+                for (int i = 7; i >= 0; --i) {
+                    if (cum + c[i] >= remaining) { d = 8 * lane + i; rem = remaining - cum; break; }
+                    cum += c[i];
                 }
             }
-            __syncthreads();
+            if (where) {
+                const int src = __ffs(where) - 1;
+                d = __shfl_sync(0xffffffffu, d, src);
+                rem = __shfl_sync(0xffffffffu, rem, src);
+            }                                 // (a lane always finds it: at least `remaining` keys match the prefix)
+            prefix |= (uint32_t)d << shift;
+            remaining = rem;
+            prefix_mask |= 255u << shift;
+            __syncwarp();
         }
-        if (threadIdx.x == 0 && rng) {
-            if (cur_lo >= 0) rng[nrng++] = make_int2(cur_lo, cur_hi);
-            reinterpret_cast<int32_t*>(a.plan + bh * a.layout.head_bytes)[m_loc] = nrng;
+        thr = prefix;
+        ties_needed = (int)remaining;
+    }
+
+    // ordered compaction of the selected block ids (ascending), 32 candidates per step
+    int32_t* bi = a.block_index ? a.block_index + (bh * a.rows_pad + m) * a.top_k : nullptr;
+    int2* rng = nullptr;
+    if (a.plan && m < a.rows)
+        rng = reinterpret_cast<int2*>(a.plan + bh * a.layout.head_bytes + a.layout.rng_off) + plan_rng_offset(a.layout, m_loc);
+    int taken = 0, ties_seen = 0, nrng = 0;
+    int cur_lo = -1, cur_hi = -1;
+    for (int base = 0; base < n_blocks; base += 32) {
+        const int n = base + lane;
+        const bool in = n < n_blocks;
+        const uint32_t key = in ? keys[n] : 0u;
+        const bool tie = in && k < n_blocks && key == thr;
+        const unsigned tb = __ballot_sync(0xffffffffu, tie);
+        const int tie_rank = ties_seen + __popc(tb & lt);
+        const bool take = in && (k >= n_blocks || key > thr || (tie && tie_rank < ties_needed));
+        unsigned word = __ballot_sync(0xffffffffu, take);
+        if (take && bi) bi[taken + __popc(word & lt)] = n;
+        taken += __popc(word);
+        ties_seen += __popc(tb);
+        if (rng) {
+            while (word) {                    // runs of ones, cut out of the ballot word with bit scans (every lane alike)
+                const int lo = __ffs(word) - 1;
+                const unsigned inv = ~(word >> lo);
+                const int len = inv ? __ffs(inv) - 1 : 32 - lo;
+                const int first = (base + lo) * 64;
+                if (first == cur_hi) cur_hi += 64 * len;
+                else {
+                    if (cur_lo >= 0) { if (lane == 0) rng[nrng] = make_int2(cur_lo, cur_hi); ++nrng; }
+                    cur_lo = first; cur_hi = first + 64 * len;
+                }
+                word = lo + len >= 32 ? 0u : word & ~((1u << (lo + len)) - 1u);
+            }
         }
-        if (a.plan && m < a.rows) {
-            uint32_t* wb = reinterpret_cast<uint32_t*>(a.plan + bh * a.layout.head_bytes + a.layout.bits_off) + (size_t)m_loc * a.layout.words_v;
-            for (int w = threadIdx.x; w < a.layout.words_v; w += blockDim.x) wb[w] = 0u;
-        }
-        // tail of the reference-format row: the reference holds arbitrary masked block ids there
-        // (ties among -inf scores); the first causally masked ids in ascending order are used here
-        if (bi) {
-            for (int j = k + threadIdx.x; j < a.top_k; j += blockDim.x) bi[j] = min(n_blocks + (j - k), a.rows_pad - 1);
-        }
-        __syncthreads();
+    }
+    if (rng) {
+        if (cur_lo >= 0) { if (lane == 0) rng[nrng] = make_int2(cur_lo, cur_hi); ++nrng; }
+        if (lane == 0) reinterpret_cast<int32_t*>(a.plan + bh * a.layout.head_bytes)[m_loc] = nrng;
+    }
+    if (a.plan && m < a.rows) {
+        uint32_t* wb = reinterpret_cast<uint32_t*>(a.plan + bh * a.layout.head_bytes + a.layout.bits_off) + (size_t)m_loc * a.layout.words_v;
+        for (int w = lane; w < a.layout.words_v; w += 32) wb[w] = 0u;
+    }
+    // tail of the reference-format row: the reference holds arbitrary masked block ids there
+    // (ties among -inf scores); the first causally masked ids in ascending order are used here
+    if (bi) {
+        for (int j = k + lane; j < a.top_k; j += 32) bi[j] = min(n_blocks + (j - k), a.rows_pad - 1);
     }
 }
 
@@ -284,7 +282,7 @@ extern "C" int minf_block_sparse_build_plan(
     const int rows_pad = bs_rows_pad(context_size);
     const int k_eff = top_k < rows_pad ? top_k : rows_pad;
     if (plan && cap_s < k_eff) return fail(MINF_E_ARG, "cap_s=%d is smaller than top_k=%d", cap_s, k_eff);
-    if ((size_t)rows_pad * 2 * kBsRows > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
+    if ((size_t)rows_pad * 2 * 4 > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
     for (int i = 0; i < 3; ++i)
         if (q_strides[i] % 4 || k_strides[i] % 4) return fail(MINF_E_ARG, "strides must be multiples of 4 elements");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -309,9 +307,10 @@ extern "C" int minf_block_sparse_build_plan(
     s.plan = static_cast<unsigned char*>(plan);
     s.layout = make_plan_layout(context_size, cap_v, cap_s);
     s.m_base = 0; s.rows_q = rows_pad;
-    const size_t smem = (size_t)rows_pad * kBsRows * sizeof(uint16_t);
+    s.rows_per_cta = (size_t)rows_pad * 2 * kBsRowsMax <= 100 * 1024 ? kBsRowsMax : 4;
+    const size_t smem = (size_t)rows_pad * s.rows_per_cta * sizeof(uint16_t);
     MINF_CUDA_OK(cudaFuncSetAttribute(bs_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bs_select_kernel<<<dim3((rows_pad + kBsRows - 1) / kBsRows, hq, batch), 256, smem, st>>>(s);
+    bs_select_kernel<<<dim3((rows_pad + s.rows_per_cta - 1) / s.rows_per_cta, hq, batch), 256, smem, st>>>(s);
     MINF_LAUNCH_OK("bs_select_kernel");
     return MINF_OK;
 }
@@ -344,7 +343,7 @@ extern "C" int minf_block_sparse_select_window(
     const int rows_loc = (n_q + 63) / 64;
     const int k_eff = top_k < bs_rows_pad(context_size) ? top_k : bs_rows_pad(context_size);
     if (cap_s < k_eff) return fail(MINF_E_ARG, "cap_s=%d is smaller than top_k=%d", cap_s, k_eff);
-    if ((size_t)rows_k * 2 * kBsRows > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
+    if ((size_t)rows_k * 2 * 4 > 200 * 1024) return fail(MINF_E_UNSUPPORTED, "context too long for the block score buffer");
     BsSelectArgs s{};
     s.qpool = static_cast<const __nv_bfloat16*>(q_pooled); s.kpool = static_cast<const __nv_bfloat16*>(k_pooled);
     s.batch = batch; s.hq = hq; s.hkv = hkv; s.n_ctx = context_size;
@@ -354,9 +353,10 @@ extern "C" int minf_block_sparse_select_window(
     s.plan = static_cast<unsigned char*>(plan);
     s.layout = make_plan_layout_window(q_pos0 / 64, rows_loc, cap_v, cap_s);
     s.m_base = q_pos0 / 64; s.rows_q = rows_loc;
-    const size_t smem = (size_t)rows_k * kBsRows * sizeof(uint16_t);
+    s.rows_per_cta = (size_t)rows_k * 2 * kBsRowsMax <= 100 * 1024 ? kBsRowsMax : 4;
+    const size_t smem = (size_t)rows_k * s.rows_per_cta * sizeof(uint16_t);
     MINF_CUDA_OK(cudaFuncSetAttribute(bs_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    bs_select_kernel<<<dim3((rows_loc + kBsRows - 1) / kBsRows, hq, batch), 256, smem, static_cast<cudaStream_t>(stream)>>>(s);
+    bs_select_kernel<<<dim3((rows_loc + s.rows_per_cta - 1) / s.rows_per_cta, hq, batch), 256, smem, static_cast<cudaStream_t>(stream)>>>(s);
     MINF_LAUNCH_OK("bs_select_kernel");
     return MINF_OK;
 }
