@@ -110,7 +110,8 @@ __global__ void __launch_bounds__(256) bs_select_kernel(const BsSelectArgs a) {
         for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int i = 0; i < 16; ++i) q[r][i] = qv[r][16 * part + i];
-        for (int n0 = warp * 4; n0 < n_max; n0 += 32) {
+#pragma unroll 2
+        for (int n0 = warp * 4; n0 < n_max; n0 += 32) {      // two steps in flight: the loads of the second overlap the first
             const int n = n0 + sub;
             uint4 raw[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
             if (n < n_max) {
