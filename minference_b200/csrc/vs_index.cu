@@ -21,7 +21,8 @@
 //   vs_plan_kernel -- merged [start,end) ranges + a bit mask over the vertical list
 //           (plan_layout.h).  The gaps of the slash list do not depend on the row block, so a
 //           CTA compacts the positions whose gap exceeds 64 once and each of its 32 row blocks
-//           walks only those; the bit mask is built in shared memory, two words per step.
+//           walks only those, writing its ranges; the bit mask is then built in shared memory in
+//           one sweep over the written ranges, 32 ranges and 32 columns at a time.
 #include <climits>
 
 #include "common.h"
@@ -202,31 +203,14 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
             if (i0 == nnz_s && lane == 0) atomicAdd(a.status + MINF_ST_NO_SLASH, 1);
         }
         if (i0 < nnz_s) {
-            // (Marking the columns of 32 ranges at a time from two binary searches per range was measured too:
-            // 0.55 ms against 0.48 ms for this scan at 131072 tokens, and slower on scattered lists as well.)
-            // close range [rs, re): record it, then advance through the verticals; the columns below
-            // rs that no earlier range covered are gathered: their bits span at most two words
+            // The ranges depend on the slash list only: they are written first, and the columns are marked afterwards
+            // in one sweep over the written ranges, 32 at a time (see below).  (Marking while walking -- a scan of the
+            // vertical list per range -- and two binary searches per range were both measured: slower.)
             auto close_range = [&](int rs, int re) {
                 // row block m of the sequence holds at most min(cap_s, m + 2) ranges (plan_layout.h)
                 if (lane == 0 && MINF_IN_BOUNDS(a.status, nrng < min(a.cap_s, a.rb_base + m + 2) && rs >= 0 && re > rs))
                     rng[nrng] = make_int2(rs, re);
                 ++nrng;
-                for (;;) {
-                    const int i = vp + lane;
-                    const int val = i < nnz_v ? v_list[i] : INT_MAX;
-                    const int n_below = __popc(__ballot_sync(0xffffffffu, val < rs));
-                    if (n_below && lane == 0) {
-                        const int lo = vp, hi = vp + n_below;
-                        const int w0 = lo >> 5, w1 = (hi - 1) >> 5;
-                        const int top = min(hi - 32 * w0, 32);
-                        if (!MINF_IN_BOUNDS(a.status, w1 < words_v)) break;
-                        wb[w0] |= (top == 32 ? 0xffffffffu : ((1u << top) - 1u)) & ~((1u << (lo & 31)) - 1u);
-                        if (w1 != w0) wb[w1] |= (hi - 32 * w1 == 32) ? 0xffffffffu : ((1u << (hi - 32 * w1)) - 1u);
-                    }
-                    const int n_inside = __popc(__ballot_sync(0xffffffffu, val < re));
-                    vp += n_inside;
-                    if (n_inside < 32) break;
-                }
             };
             // first gap position after i0
             int lo = 0, hi = n_cand;
@@ -245,7 +229,7 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
                 unsigned todo = __ballot_sync(0xffffffffu, valid && (e - prev > 64));
                 // Scattered lists: every candidate of the batch opens a range of its own.  Lane l then knows the
                 // range it closes without waiting for the others -- it starts at the previous candidate's tile --
-                // so the whole batch is written with one store per lane and its columns are marked in one sweep.
+                // so the whole batch is written with one store per lane.
                 const unsigned all_valid = __ballot_sync(0xffffffffu, valid);    // lanes 0..cnt-1
                 const int cnt = __popc(all_valid);
                 if (todo == all_valid && cnt > 1) {
@@ -253,35 +237,11 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
                     if (lane == 0) ef = e_first;
                     const int re_l = ef + ((prev - ef + 63) & ~63);
                     if (__ballot_sync(0xffffffffu, valid && e > re_l + 64) == all_valid) {
-                        const int rs_l = valid ? ef - 64 : INT_MAX, re_v = valid ? re_l : INT_MAX;
+                        const int rs_l = ef - 64;
                         if (valid && MINF_IN_BOUNDS(a.status, nrng + lane < min(a.cap_s, a.rb_base + m + 2) && rs_l >= 0 && re_l > rs_l))
                             rng[nrng + lane] = make_int2(rs_l, re_l);
                         nrng += cnt;
-                        const int re_last = __shfl_sync(0xffffffffu, re_l, cnt - 1);
                         e_first = __shfl_sync(0xffffffffu, e, cnt - 1);
-                        for (;;) {          // columns up to the end of the batch: gathered unless a range covers them
-                            const int i = vp + lane;
-                            const int val = i < nnz_v ? v_list[i] : INT_MAX;
-                            const bool in_batch = val < re_last;
-                            int blo = 0, bhi = cnt;                     // number of ranges of the batch starting at or below val
-#pragma unroll
-                            for (int it = 0; it < 6; ++it) {
-                                const int mid = (blo + bhi) >> 1;
-                                const int rs_mid = __shfl_sync(0xffffffffu, rs_l, mid & 31);
-                                if (blo < bhi) { if (rs_mid <= val) blo = mid + 1; else bhi = mid; }
-                            }
-                            const int re_before = __shfl_sync(0xffffffffu, re_v, max(blo - 1, 0));
-                            const bool covered = blo > 0 && val < re_before;
-                            const unsigned marks = __ballot_sync(0xffffffffu, in_batch && !covered);
-                            const int n_in = __popc(__ballot_sync(0xffffffffu, in_batch));
-                            if (marks && lane == 0) {
-                                const int w0 = vp >> 5, sh = vp & 31;
-                                if (MINF_IN_BOUNDS(a.status, w0 < words_v)) wb[w0] |= marks << sh;
-                                if (sh && (marks >> (32 - sh)) && MINF_IN_BOUNDS(a.status, w0 + 1 < words_v)) wb[w0 + 1] |= marks >> (32 - sh);
-                            }
-                            vp += n_in;
-                            if (n_in < 32) break;
-                        }
                         todo = 0u;
                     }
                 }
@@ -298,6 +258,40 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
             }
             const int e_last = max(end_m - s_list[nnz_s - 1], 64);
             close_range(e_first - 64, e_first + ((e_last - e_first + 63) & ~63));
+            // Columns: a vertical index is gathered iff it lies below the end of the last range and in none of the
+            // ranges.  Both lists ascend, so the ranges are taken 32 at a time (one per lane) and the verticals up to
+            // the end of the group 32 at a time: each finds the range that starts at or below it by a binary search
+            // over the lanes.
+            __syncwarp();                     // the ranges written above are read back here
+            const int n_read = min(nrng, min(a.cap_s, a.rb_base + m + 2));
+            for (int g = 0; g < n_read; g += 32) {
+                const int cnt = min(32, n_read - g);
+                const int2 mine = lane < cnt ? rng[g + lane] : make_int2(INT_MAX, INT_MAX);
+                const int re_last = __shfl_sync(0xffffffffu, mine.y, cnt - 1);
+                for (;;) {
+                    const int i = vp + lane;
+                    const int val = i < nnz_v ? v_list[i] : INT_MAX;
+                    const bool in_group = val < re_last;
+                    int blo = 0, bhi = cnt;         // number of ranges of the group starting at or below val
+#pragma unroll
+                    for (int it = 0; it < 6; ++it) {
+                        const int mid = (blo + bhi) >> 1;
+                        const int rs_mid = __shfl_sync(0xffffffffu, mine.x, mid & 31);
+                        if (blo < bhi) { if (rs_mid <= val) blo = mid + 1; else bhi = mid; }
+                    }
+                    const int re_before = __shfl_sync(0xffffffffu, mine.y, max(blo - 1, 0));
+                    const bool covered = blo > 0 && val < re_before;
+                    const unsigned marks = __ballot_sync(0xffffffffu, in_group && !covered);
+                    const int n_in = __popc(__ballot_sync(0xffffffffu, in_group));
+                    if (marks && lane == 0) {
+                        const int w0 = vp >> 5, sh = vp & 31;
+                        if (MINF_IN_BOUNDS(a.status, w0 < words_v)) wb[w0] |= marks << sh;
+                        if (sh && (marks >> (32 - sh)) && MINF_IN_BOUNDS(a.status, w0 + 1 < words_v)) wb[w0 + 1] |= marks >> (32 - sh);
+                    }
+                    vp += n_in;
+                    if (n_in < 32) break;
+                }
+            }
         }
         __syncwarp();
         if (lane == 0) reinterpret_cast<int32_t*>(slot)[m] = nrng;
