@@ -534,7 +534,7 @@ def run_gpu_arm(args, wl):
             torch.cuda.empty_cache()
             detail["one_gpu_1m"] = side_measurement("llama3_8b_1m_vs", dev, steps=2, warmup=1)
             torch.cuda.empty_cache()
-            detail["one_gpu_1m_band"] = side_measurement("llama3_8b_1m_vs_local", dev, steps=2, warmup=1)
+            detail["one_gpu_1m_band"] = side_measurement("llama3_8b_1m_vs_local", dev, steps=3, warmup=3)   # short steps: settle the allocator first
         if flex:
             detail["blocks_selected_of_causal"] = float(box["block_mask"].sum().item()) / (hq * (n // 128) * (n // 128 + 1) / 2)
             cpu_tf, cpu_desc = None, "not timed for this workload (the default workload carries the CPU baseline)"
