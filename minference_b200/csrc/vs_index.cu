@@ -264,7 +264,30 @@ __global__ void __launch_bounds__(kConvertWarps * 32) vs_plan_kernel(const Conve
             // over the lanes.
             __syncwarp();                     // the ranges written above are read back here
             const int n_read = min(nrng, min(a.cap_s, a.rb_base + m + 2));
-            for (int g = 0; g < n_read; g += 32) {
+            if (n_read <= 8) {
+                // few ranges (dense index sets): two warp-uniform binary searches per range, then every lane fills
+                // one word of the bit mask
+                int settled = 0;                    // vertical entries below it are done
+                for (int g = 0; g < n_read; ++g) {
+                    const int2 rg = rng[g];
+                    int lo = settled, hi = nnz_v;
+                    while (lo < hi) { const int mid = (lo + hi) >> 1; if (v_list[mid] < rg.x) lo = mid + 1; else hi = mid; }
+                    const int below = lo;           // entries [settled, below) lie under the range: gathered
+                    hi = nnz_v;
+                    while (lo < hi) { const int mid = (lo + hi) >> 1; if (v_list[mid] < rg.y) lo = mid + 1; else hi = mid; }
+                    if (settled < below) {
+                        for (int w = (settled >> 5) + lane; w <= ((below - 1) >> 5); w += 32) {
+                            if (!MINF_IN_BOUNDS(a.status, w < words_v)) break;
+                            const int l = max(settled - 32 * w, 0), h = min(below - 32 * w, 32);
+                            wb[w] |= (h == 32 ? 0xffffffffu : ((1u << h) - 1u)) & ~((1u << l) - 1u);
+                        }
+                    }
+                    __syncwarp();
+                    settled = lo;                   // entries inside the range are skipped
+                }
+                vp = settled;
+            }
+            for (int g = 0; n_read > 8 && g < n_read; g += 32) {
                 const int cnt = min(32, n_read - g);
                 const int2 mine = lane < cnt ? rng[g + lane] : make_int2(INT_MAX, INT_MAX);
                 const int re_last = __shfl_sync(0xffffffffu, mine.y, cnt - 1);
