@@ -151,3 +151,44 @@ def test_install_on_model_wraps_every_attention_layer():
     assert V.install_on_model(model, {"best_pattern": [{}, {}], "starting_layer": 0}) == 2
     assert all(m.impl._minference_b200_wrapped for m in model if isinstance(m, Attn))
     assert model[0].impl.forward(None, None, None, None, None, None, None) == "stock"       # no metadata: profiling run
+
+
+def test_vllm_hook_on_the_installed_vllm_implementation_and_metadata_classes(dev):
+    """The same single-sequence prefill through an object of the installed vLLM's own ``FlashAttentionImpl`` with its
+    own ``FlashAttentionMetadata`` (no engine, no KV cache: the wrapped method takes the sparse path before the stock
+    code would touch either)."""
+    import inspect
+
+    try:
+        from vllm.v1.attention.backends.flash_attn import FlashAttentionImpl, FlashAttentionMetadata
+    except Exception as e:
+        pytest.skip(f"vLLM cannot be imported here: {type(e).__name__}")
+    from minference_b200 import vllm_hook as V
+    from minference_b200.modules.minference_forward import minference_prefill_forward
+    from minference_b200.synthetic import make_qkv
+
+    n, hq, hkv = 2048 + 40, 4, 2
+    q, k, v = (t.to(dev) for t in make_qkv(n, hq, hkv, seed=18, dtype=torch.bfloat16))
+    table = [{"0": ["vertical_and_slash", 100, 400, 1.0], "1": ["stream_llm", 64, 512, 1.0], "2": ["block_sparse", 0, 0, 1.0]}]
+    attn_config = {"best_pattern": table, "starting_layer": 0}
+    want = minference_prefill_forward(q, k, v, {"attn_forward_config": dict(attn_config), "layer_idx": 0,
+                                               "num_hidden_layers": 1, "attention_mask": None})
+    try:
+        kwargs = dict(num_heads=hq, head_size=128, scale=128 ** -0.5, num_kv_heads=hkv, alibi_slopes=None, sliding_window=None,
+                      kv_cache_dtype="auto")
+        accepted = inspect.signature(FlashAttentionImpl.__init__).parameters
+        impl = FlashAttentionImpl(**{a: b for a, b in kwargs.items() if a in accepted})
+        md = FlashAttentionMetadata(
+            num_actual_tokens=n, max_query_len=n, query_start_loc=torch.tensor([0, n], dtype=torch.int32, device=dev),
+            max_seq_len=n, seq_lens=torch.tensor([n], dtype=torch.int32, device=dev),
+            block_table=torch.zeros(1, 1, dtype=torch.int32, device=dev), slot_mapping=torch.zeros(n, dtype=torch.int64, device=dev),
+            use_cascade=False, common_prefix_len=0, cu_prefix_query_lens=None, prefix_kv_lens=None, suffix_kv_lens=None)
+    except Exception as e:           # constructor arguments of another vLLM version, or a missing engine context
+        pytest.skip(f"the installed vLLM's classes cannot be built stand-alone: {type(e).__name__}: {e}")
+    assert V.is_single_sequence_prefill(md) and V.supports(impl, q)
+    V.wrap_impl(impl, dict(attn_config), head_offset=0)
+    layer = types.SimpleNamespace(layer_name="model.layers.0.self_attn.attn")
+    tok = lambda x: x[0].transpose(0, 1).contiguous()
+    out = torch.empty(n, hq * 128, dtype=torch.bfloat16, device=dev)
+    impl.forward(layer, tok(q), tok(k), tok(v), None, md, out)
+    assert torch.equal(out.view(n, hq, 128).transpose(0, 1)[None], want)

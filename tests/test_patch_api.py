@@ -264,3 +264,28 @@ def test_zigzag_positions_cover_the_sequence():
     allpos = torch.cat([zigzag_positions(n, r, world) for r in range(world)])
     assert sorted(allpos.tolist()) == list(range(n))
     assert zigzag_positions(n, 0, world)[-1].item() == n - 1      # the last token is rank 0's last token
+
+
+def test_vllm_hook_assumptions_hold_for_the_installed_vllm():
+    """The hook wraps ``impl.forward`` of every attention layer and reads a few host-side metadata fields: the installed
+    vLLM's FlashAttention implementation, its metadata and its attention layer are inspected (no GPU, no engine) for
+    exactly the names the hook relies on."""
+    import dataclasses
+    import inspect
+
+    import pytest
+
+    try:
+        from vllm.model_executor.layers.attention import Attention
+        from vllm.v1.attention.backends.flash_attn import FlashAttentionImpl, FlashAttentionMetadata
+    except Exception as e:           # vLLM absent or not importable on this machine
+        pytest.skip(f"vLLM cannot be imported here: {type(e).__name__}")
+    params = list(inspect.signature(FlashAttentionImpl.forward).parameters)
+    assert params[:8] == ["self", "layer", "query", "key", "value", "kv_cache", "attn_metadata", "output"]
+    fields = {f.name for f in dataclasses.fields(FlashAttentionMetadata)}
+    assert {"num_actual_tokens", "max_query_len", "query_start_loc", "max_seq_len", "use_cascade", "causal"} <= fields
+    init_src = inspect.getsource(FlashAttentionImpl.__init__)
+    for attr in ("num_heads", "num_kv_heads", "head_size", "scale", "sliding_window", "logits_soft_cap", "alibi_slopes"):
+        assert f"self.{attr}" in init_src, attr
+    layer_src = inspect.getsource(Attention.__init__)
+    assert "self.impl" in layer_src and "self.layer_name" in layer_src
