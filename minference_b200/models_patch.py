@@ -28,8 +28,9 @@ class MInference:
         return self.patch_model(model)
 
     def patch_model(self, model):
-        model.config.starting_layer = self.config.starting_layer
-        model.config.config_path = self.config.config_path
+        if hasattr(model, "config"):          # a Hugging Face model; a vllm.LLM carries no config object of this kind
+            model.config.starting_layer = self.config.starting_layer
+            model.config.config_path = self.config.config_path
         kw = self.config.attn_kwargs
         ty = self.config.attn_type
 

@@ -37,12 +37,24 @@ def layer_index_of(layer_name: str) -> int:
 
 def is_single_sequence_prefill(attn_metadata) -> bool:
     """One sequence whose tokens are all new: no cached context, no other request in the batch.  Only host-side
-    fields of the metadata are read (no device synchronisation)."""
-    if attn_metadata is None or getattr(attn_metadata, "use_cascade", False) or not getattr(attn_metadata, "causal", True):
-        return False
-    n = attn_metadata.num_actual_tokens
-    return (attn_metadata.query_start_loc.shape[0] == 2 and n > 1 and attn_metadata.max_query_len == n
-            and attn_metadata.max_seq_len == n)
+    fields of the metadata are read (no device synchronisation).  Two layouts of the metadata are known: the
+    FlashAttention backend's (query offsets, longest query, longest sequence) and the FlashInfer backend's, the default
+    on this GPU generation (counts of prefill and decode requests and of their tokens; it does not say how long the
+    cached context is, which is why ``patch_vllm`` insists on an engine without prefix caching and chunked prefill).
+    Anything else is not taken."""
+    try:
+        if attn_metadata is None or getattr(attn_metadata, "use_cascade", False) or not getattr(attn_metadata, "causal", True):
+            return False
+        n = attn_metadata.num_actual_tokens
+        if hasattr(attn_metadata, "query_start_loc"):
+            return (attn_metadata.query_start_loc.shape[0] == 2 and n > 1 and attn_metadata.max_query_len == n
+                    and attn_metadata.max_seq_len == n)
+        if hasattr(attn_metadata, "num_prefills"):
+            return (attn_metadata.num_prefills == 1 and getattr(attn_metadata, "num_decodes", 0) == 0
+                    and getattr(attn_metadata, "num_prefill_tokens", n) == n and n > 1)
+    except AttributeError:
+        pass
+    return False
 
 
 def sparse_prefill_forward(impl, layer, query, key, value, output, attn_metadata, attn_config: dict, head_offset: int,
@@ -105,6 +117,20 @@ def install_on_model(model, attn_config: dict) -> int:
     return count
 
 
+def check_engine_settings(llm) -> None:
+    """The sparse path sees a prompt only if it arrives as one batch with nothing cached: refuse an engine with prefix
+    caching, or with chunked prefill and a token budget below its longest prompt.  Engines whose configuration objects
+    are laid out differently are let through (the per-batch test still applies)."""
+    cfg = getattr(getattr(llm, "llm_engine", None), "vllm_config", None)
+    cache, sched, model = (getattr(cfg, name, None) for name in ("cache_config", "scheduler_config", "model_config"))
+    if getattr(cache, "enable_prefix_caching", False):
+        raise ValueError("the sparse prefill needs an engine with enable_prefix_caching=False")
+    budget, longest = getattr(sched, "max_num_batched_tokens", None), getattr(model, "max_model_len", None)
+    if getattr(sched, "enable_chunked_prefill", False) and budget and longest and budget < longest:
+        raise ValueError(f"the sparse prefill needs whole prompts in one batch: max_num_batched_tokens={budget} is below "
+                         f"max_model_len={longest} with chunked prefill on")
+
+
 def patch_vllm(llm, config):
     """``MInference("vllm_minference", model_name)(llm)``: install the hook in every worker of a ``vllm.LLM``."""
     attn_config = dict(config.attn_kwargs)
@@ -114,6 +140,8 @@ def patch_vllm(llm, config):
     attn_config.setdefault("starting_layer", 0)
     if attn_config["starting_layer"] < 0:
         attn_config["starting_layer"] = 0
+
+    check_engine_settings(llm)
 
     def install(model):     # shipped to the workers
         from minference_b200.vllm_hook import install_on_model

@@ -289,3 +289,47 @@ def test_vllm_hook_assumptions_hold_for_the_installed_vllm():
         assert f"self.{attr}" in init_src, attr
     layer_src = inspect.getsource(Attention.__init__)
     assert "self.impl" in layer_src and "self.layer_name" in layer_src
+    # the FlashInfer backend (the default on Blackwell): same forward signature, its own metadata layout
+    from vllm.v1.attention.backends.flashinfer import FlashInferBackend, FlashInferImpl, FlashInferMetadata
+    from vllm.v1.attention.backends.flash_attn import FlashAttentionBackend
+
+    assert list(inspect.signature(FlashInferImpl.forward).parameters)[:8] == params[:8]
+    fi = {f.name for f in dataclasses.fields(FlashInferMetadata)}
+    assert {"num_actual_tokens", "num_prefills", "num_decodes", "num_prefill_tokens", "use_cascade"} <= fi
+    # the layer, not impl.forward, writes the KV cache: a wrapped forward that skips the stock code leaves it filled
+    assert FlashAttentionBackend.forward_includes_kv_cache_update is False
+    assert FlashInferBackend.forward_includes_kv_cache_update is False
+
+
+def test_vllm_hook_recognises_both_metadata_layouts_and_refuses_unsuitable_engines():
+    import types
+
+    import pytest
+    import torch
+
+    from minference_b200 import vllm_hook as V
+
+    fa = types.SimpleNamespace(num_actual_tokens=100, query_start_loc=torch.tensor([0, 100]), max_query_len=100, max_seq_len=100,
+                               use_cascade=False, causal=True)
+    assert V.is_single_sequence_prefill(fa)
+    assert not V.is_single_sequence_prefill(types.SimpleNamespace(**{**vars(fa), "max_seq_len": 300}))       # cached context
+    fi = types.SimpleNamespace(num_actual_tokens=100, num_prefills=1, num_decodes=0, num_prefill_tokens=100, use_cascade=False)
+    assert V.is_single_sequence_prefill(fi)
+    assert not V.is_single_sequence_prefill(types.SimpleNamespace(**{**vars(fi), "num_decodes": 2, "num_prefill_tokens": 98}))
+    assert not V.is_single_sequence_prefill(types.SimpleNamespace(**{**vars(fi), "num_prefills": 2}))
+    assert not V.is_single_sequence_prefill(types.SimpleNamespace(num_actual_tokens=100))                     # unknown layout
+    assert not V.is_single_sequence_prefill(None)
+
+    def engine(prefix, chunked, budget, longest):
+        cfg = types.SimpleNamespace(cache_config=types.SimpleNamespace(enable_prefix_caching=prefix),
+                                    scheduler_config=types.SimpleNamespace(enable_chunked_prefill=chunked, max_num_batched_tokens=budget),
+                                    model_config=types.SimpleNamespace(max_model_len=longest))
+        return types.SimpleNamespace(llm_engine=types.SimpleNamespace(vllm_config=cfg))
+
+    V.check_engine_settings(engine(False, False, 8192, 8192))
+    V.check_engine_settings(engine(False, True, 8192, 8192))
+    V.check_engine_settings(types.SimpleNamespace())                   # unknown engine object: let through
+    with pytest.raises(ValueError):
+        V.check_engine_settings(engine(True, False, 8192, 8192))
+    with pytest.raises(ValueError):
+        V.check_engine_settings(engine(False, True, 2048, 8192))
