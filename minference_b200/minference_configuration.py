@@ -2,8 +2,9 @@
 
 Only the attention types that run on this library's kernels are accepted: the dynamic sparse
 prefill ("minference", also with ``is_search=True`` for the offline pattern search; "vllm_minference"
-for the vLLM hook), its static variant ("static"), the fixed index sets "dilated1" / "dilated2", the
-fixed A-shape pattern ("a_shape"), A-shape with dense last rows ("tri_shape"), the TriangleMix layer
+for the vLLM hook, which also takes "vllm_a_shape", "vllm_tri_shape" and "vllm_flexprefill"), its static
+variant ("static"), the fixed index sets "dilated1" / "dilated2", the fixed A-shape pattern ("a_shape"),
+A-shape with dense last rows ("tri_shape"), the TriangleMix layer
 policies ("tri_mix", "tri_mix_minference"), FlexPrefill's adaptive block budgets ("flexprefill"; ``attn_kwargs``: gamma,
 tau, min_budget, max_budget, block_size) and dense causal ("dense").  The KV-cache methods of the
 reference (kv_type other than "dense") are decode-side features outside this library.
@@ -15,7 +16,8 @@ from .configs.model2path import MODEL2PATH
 
 class MInferenceConfig:
     MINFERENCE_ATTENTION_TYPES = ["minference", "vllm_minference", "tri_mix_minference"]      # need a pattern table
-    OTHER_ATTENTION_TYPES = ["dense", "static", "dilated1", "dilated2", "a_shape", "tri_shape", "tri_mix", "flexprefill"]
+    OTHER_ATTENTION_TYPES = ["dense", "static", "dilated1", "dilated2", "a_shape", "tri_shape", "tri_mix", "flexprefill",
+                             "vllm_a_shape", "vllm_tri_shape", "vllm_flexprefill"]
     KV_TYPES = ["dense"]
 
     def __init__(

@@ -33,6 +33,9 @@ class MInference:
             model.config.config_path = self.config.config_path
         kw = self.config.attn_kwargs
         ty = self.config.attn_type
+        for_vllm = ty.startswith("vllm_")
+        if for_vllm and ty != "vllm_minference":        # same defaults as the Hugging Face type of that name
+            ty = ty[len("vllm_"):]
 
         def load_table():       # the pattern table is loaded once here (models_patch.py:98-102 of the reference)
             if "best_pattern" not in kw:
@@ -63,7 +66,7 @@ class MInference:
         elif ty == "static":
             if self.config.config_path:       # budgets of head 0 come from the table; without one the default (1000, 6096)
                 load_table()
-        if ty == "vllm_minference":
+        if for_vllm:
             from .vllm_hook import patch_vllm
 
             return patch_vllm(model, self.config)

@@ -68,9 +68,17 @@ def sparse_prefill_forward(impl, layer, query, key, value, output, attn_metadata
     v = value[:n].view(n, hkv, d).transpose(0, 1).unsqueeze(0)
     if layer_idx is None:
         layer_idx = layer_index_of(getattr(layer, "layer_name", ""))
-    out = minference_prefill_forward(q, k, v, {"attention_mask": None, "layer_idx": layer_idx, "head_offset": head_offset,
-                                               "num_hidden_layers": len(attn_config.get("best_pattern", [])),
-                                               "attn_forward_config": attn_config})
+    # "vllm_minference" runs the per-head pattern table; "vllm_a_shape", "vllm_tri_shape" and "vllm_flexprefill" (the
+    # reference's other vLLM types, minference_configuration.py:24-28) the operator of that name, which has no table
+    kind = attn_config.get("prefill_operator", "minference")
+    if kind == "minference":
+        forward = minference_prefill_forward
+    else:
+        from .patch import prefill_forwards
+
+        forward = prefill_forwards[kind]
+    out = forward(q, k, v, {"attention_mask": None, "layer_idx": layer_idx, "head_offset": head_offset,
+                            "num_hidden_layers": len(attn_config.get("best_pattern", [])), "attn_forward_config": attn_config})
     output[:n].view(n, h, d).copy_(out[0].transpose(0, 1))
     return output
 
@@ -134,7 +142,8 @@ def check_engine_settings(llm) -> None:
 def patch_vllm(llm, config):
     """``MInference("vllm_minference", model_name)(llm)``: install the hook in every worker of a ``vllm.LLM``."""
     attn_config = dict(config.attn_kwargs)
-    if "best_pattern" not in attn_config:
+    attn_config["prefill_operator"] = config.attn_type[len("vllm_"):] if config.attn_type.startswith("vllm_") else config.attn_type
+    if attn_config["prefill_operator"] == "minference" and "best_pattern" not in attn_config:
         with open(config.config_path) as f:
             attn_config["best_pattern"] = json.load(f)
     attn_config.setdefault("starting_layer", 0)

@@ -192,3 +192,33 @@ def test_vllm_hook_on_the_installed_vllm_implementation_and_metadata_classes(dev
     out = torch.empty(n, hq * 128, dtype=torch.bfloat16, device=dev)
     impl.forward(layer, tok(q), tok(k), tok(v), None, md, out)
     assert torch.equal(out.view(n, hq, 128).transpose(0, 1)[None], want)
+
+
+def test_vllm_hook_runs_the_other_operators_by_name(dev):
+    """``vllm_a_shape`` and ``vllm_flexprefill``: the wrapped forward hands the tokens to the operator of that name."""
+    from minference_b200 import vllm_hook as V
+    from minference_b200.modules.flexprefill import flexprefill_forward
+    from minference_b200.ops.streaming_kernel import a_shape_kernel
+    from minference_b200.synthetic import make_qkv
+
+    n, hq, hkv = 2500, 4, 2
+    q, k, v = (t.to(dev) for t in make_qkv(n, hq, hkv, seed=19, dtype=torch.bfloat16))
+    md = types.SimpleNamespace(num_actual_tokens=n, num_prefills=1, num_decodes=0, num_prefill_tokens=n, use_cascade=False)
+    layer = types.SimpleNamespace(layer_name="model.layers.0.self_attn.attn")
+    tok = lambda x: x[0].transpose(0, 1).contiguous()
+
+    class Impl:
+        def __init__(self):
+            self.num_heads, self.num_kv_heads, self.head_size, self.scale = hq, hkv, 128, 128 ** -0.5
+            self.alibi_slopes, self.sliding_window, self.logits_soft_cap, self.sinks = None, (-1, -1), 0, None
+
+        def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None):
+            raise AssertionError("the stock method must not run for a single-sequence prefill")
+
+    for cfg, op in (({"prefill_operator": "a_shape", "n_local": 512, "n_init": 64}, a_shape_kernel),
+                    ({"prefill_operator": "flexprefill", "gamma": 0.8, "tau": 0.0}, flexprefill_forward)):
+        want = op(q, k, v, {"attn_forward_config": dict(cfg), "layer_idx": 0, "num_hidden_layers": 1, "attention_mask": None})
+        impl = V.wrap_impl(Impl(), dict(cfg), 0)
+        out = torch.empty(n, hq * 128, dtype=torch.bfloat16, device=dev)
+        impl.forward(layer, tok(q), tok(k), tok(v), None, md, out)
+        assert torch.equal(out.view(n, hq, 128).transpose(0, 1)[None], want)

@@ -333,3 +333,36 @@ def test_vllm_hook_recognises_both_metadata_layouts_and_refuses_unsuitable_engin
         V.check_engine_settings(engine(True, False, 8192, 8192))
     with pytest.raises(ValueError):
         V.check_engine_settings(engine(False, True, 2048, 8192))
+
+
+def test_other_vllm_attention_types_are_routed_through_the_hook_with_their_defaults():
+    """``MInference("vllm_a_shape")(llm)`` and its siblings (minference_configuration.py:24-28 of the reference): the hook
+    is installed with the operator of that name and the defaults of the Hugging Face type (no pattern table)."""
+    import types
+
+    import torch
+
+    from minference_b200 import MInference
+
+    class Impl:
+        num_heads, num_kv_heads, head_size, scale = 4, 2, 128, 128 ** -0.5
+
+        def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None):
+            return output
+
+    for ty, want in (("vllm_a_shape", {"n_local": 3968, "n_init": 128}), ("vllm_tri_shape", {"n_last": 100}),
+                     ("vllm_flexprefill", {})):
+        model = torch.nn.Module()
+        model.attn = torch.nn.Module()
+        model.attn.impl = Impl()
+        def apply_model(fn, model=model):
+            return [fn(model)]
+
+        llm = types.SimpleNamespace(apply_model=apply_model)
+        assert MInference(ty)(llm) is llm
+        assert getattr(model.attn.impl, "_minference_b200_wrapped", False)
+        cfg = model.attn.impl.forward.__func__.__closure__
+        attn_config = next(c.cell_contents for c in cfg if isinstance(c.cell_contents, dict))
+        assert attn_config["prefill_operator"] == ty[len("vllm_"):]
+        for key, val in want.items():
+            assert attn_config[key] == val
