@@ -210,3 +210,39 @@ def test_a_rank_that_fails_before_its_send_ends_the_ring_with_an_error(mode):
     outcomes = dict(result.get(timeout=10) for _ in range(world))
     assert outcomes[1].startswith("error")
     assert outcomes[0].startswith("error"), outcomes       # the healthy rank saw the failure as an exception
+
+
+def test_score_exchange_packs_each_chunk_alone_and_assembles_the_sum():
+    """The exchange of the distributed estimator on CPU tensors with a stand-in score pass that *adds* into its
+    window (as the kernel's boundary atomics do): every rank's pack must hold each of its chunks alone -- the middle
+    rank's two chunks are neighbours and share 63 diagonal offsets -- and the assembly must be the sum over chunks."""
+    import torch
+
+    from minference_b200.dist import ring
+
+    for world in (1, 2, 3, 4):
+        c = 128
+        n = 2 * world * c
+        packs = []
+        for rank in range(world):
+            chunks = ring.owned_chunks(rank, world)
+
+            def score_pass(i, vertical, slash, chunks=chunks):
+                ci = chunks[i]
+                lo, hi = ring.slash_window(n, ci, c)
+                vertical[:, :, ci * c:(ci + 1) * c] = float(ci + 1)
+                slash[:, :, lo:hi] += float(ci + 1)
+
+            packs.append(ring.rank_score_pack(score_pass, chunks, n, c, 1, 2, torch.device("cpu")))
+        scores = ring.assemble_scores(torch.stack(packs), n, c, world)
+        want_v = torch.arange(1, 2 * world + 1, dtype=torch.float32).repeat_interleave(c)
+        want_s = torch.zeros(n)
+        for ci in range(2 * world):
+            lo, hi = ring.slash_window(n, ci, c)
+            want_s[lo:hi] += ci + 1
+        assert torch.equal(scores[0], want_v.expand(1, 2, n))
+        assert torch.equal(scores[1], want_s.expand(1, 2, n))
+        # neighbouring windows do overlap, by 63 offsets
+        if world > 1:
+            (lo0, hi0), (lo1, hi1) = ring.slash_window(n, 0, c), ring.slash_window(n, 1, c)
+            assert hi1 - lo0 == 63
